@@ -94,7 +94,7 @@ class CacheGroup:
 
     def page_bytes(self, element_size: int) -> int:
         n = self.need
-        return n.kv_heads * (n.head_dim + n.v_dim) * self.page_size * element_size * len(self.entries)
+        return n.kv_heads * (n.head_dim + n.stored_v_dim) * self.page_size * element_size * len(self.entries)
 
 
 class _Table:
@@ -165,11 +165,11 @@ class CacheManager:
             for grp in self.groups:
                 n = grp.need
                 for e in grp.entries:
-                    if grp.paged and n.v_dim == n.head_dim:
+                    if grp.paged and n.stored_v_dim == n.head_dim:
                         grp.kv[e] = torch.zeros((num_pages, 2, n.kv_heads, page_size, n.head_dim),
                                                 dtype=dtype, device=self.device)
-                    elif grp.paged:     # a page holds its keys, then its values
-                        grp.kv[e] = torch.zeros((num_pages, n.kv_heads * page_size * (n.head_dim + n.v_dim)),
+                    elif grp.paged:     # a page holds its keys, then its values (none where the keys hold them)
+                        grp.kv[e] = torch.zeros((num_pages, n.kv_heads * page_size * (n.head_dim + n.stored_v_dim)),
                                                 dtype=dtype, device=self.device)
                     if n.states:
                         # Not cleared when a slot is taken again: a mixer starts from zero at position 0.

@@ -58,6 +58,9 @@ def _register_builtin() -> None:
     from .lilenex import LilenexConfig
     from ..models.lilenex import lilenex_spec
     register_architecture("Lilenex", LilenexConfig.from_dict, lilenex_spec)
+    from .sogalix import SogalixConfig
+    from ..models.sogalix import sogalix_spec
+    register_architecture("Sogalix", SogalixConfig.from_dict, sogalix_spec)
 
 
 _register_builtin()

@@ -203,7 +203,7 @@ class Engine:
         for need in entries.values():
             if need.kind in ("full", "window", "chunk"):
                 k = need.group_key()
-                per_page[k] = per_page.get(k, 0) + need.kv_heads * (need.head_dim + need.v_dim) * self.config.page_size * esize
+                per_page[k] = per_page.get(k, 0) + need.kv_heads * (need.head_dim + need.stored_v_dim) * self.config.page_size * esize
         if not per_page:
             return 1
         bytes_per_page = sum(per_page.values())   # one page in every group

@@ -28,8 +28,15 @@ class DecoderModel:
         self.rt = runtime
         self.blocks = [build_part("block", b, runtime) for b in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, runtime)
+        self.embedding_norm = build_part("norm", spec.embedding_norm, runtime) if spec.embedding_norm is not None else None
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
+
+    def _roots(self):
+        roots = [(b, s) for b, s in zip(self.blocks, self.spec.layers)] + [(self.final_norm, self.spec.final_norm)]
+        if self.embedding_norm is not None:
+            roots.append((self.embedding_norm, self.spec.embedding_norm))
+        return roots
 
     # ------------------------------------------------------------------ tensors
     def expected_tensors(self) -> Dict[str, TensorSpec]:
@@ -41,8 +48,7 @@ class DecoderModel:
             out[self.spec.lm_head] = TensorSpec((self.spec.vocab_size, self.spec.hidden_size))
         for shared in self.spec.shared_tensors.values():
             out[shared.name] = shared.spec
-        roots = [(b, s) for b, s in zip(self.blocks, self.spec.layers)] + [(self.final_norm, self.spec.final_norm)]
-        for root, rspec in roots:
+        for root, rspec in self._roots():
             for part, pspec in _walk(root, rspec):
                 for local, ts in part.tensor_specs().items():
                     out[pspec.tensors[local]] = ts
@@ -58,7 +64,7 @@ class DecoderModel:
             self.lm_head = tensors[self.spec.lm_head].to(device=rt.device, dtype=rt.dtype).contiguous()
         for key, shared in self.spec.shared_tensors.items():
             rt.shared[key] = tensors[shared.name].to(device=rt.device, dtype=rt.dtype).contiguous()
-        roots = [(b, s) for b, s in zip(self.blocks, self.spec.layers)] + [(self.final_norm, self.spec.final_norm)]
+        roots = self._roots()
         for root, rspec in roots:
             for part, pspec in _walk(root, rspec):
                 specs = part.tensor_specs()
@@ -99,6 +105,9 @@ class DecoderModel:
                 raise ValueError(f"unknown position vector {self.spec.position_vector!r}")
             x, residual = None, ops.embed_scaled(token_ids, self.embedding, self.spec.embedding_scale, ctx.positions,
                                                  self.spec.position_base if self.spec.position_vector else 0.0)
+        elif self.embedding_norm is not None:
+            # the normed rows, in float32, are the stream itself
+            x, residual = None, self.embedding_norm.start_stream(ops.embed(token_ids, self.embedding))
         else:
             x, residual = ops.embed(token_ids, self.embedding), None
         run = self.spec.run_order

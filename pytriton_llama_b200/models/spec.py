@@ -44,6 +44,7 @@ class ModelSpec:
     position_vector: Optional[str] = None   # "sinusoidal": entry 2i, 2i+1 of the stream get sin, cos(p * base^(-2i/width)) added
     position_base: float = 10000.0
     logit_softcap: float = 0.0          # > 0: logits <- cap * tanh(logits / cap)
+    embedding_norm: Optional[PartSpec] = None   # a norm part the looked-up rows pass before they become the stream
     shared_tensors: Dict[str, "SharedTensor"] = field(default_factory=dict)   # read by parts of every layer (Runtime.shared)
 
     def validate(self) -> None:

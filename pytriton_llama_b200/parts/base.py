@@ -70,7 +70,8 @@ class CacheNeed:
     ``head_dim`` (0: the same).  ``state_shape``/``state_dtype``: per-request state of fixed size
     (None if none).  ``states``: further per-request states by name, float32, as (name, shape)
     pairs; a mixer made of several lists those of all its members.  ``keep_first`` (kind "window"):
-    the keys of positions below it stay visible, and held, whatever the window has passed."""
+    the keys of positions below it stay visible, and held, whatever the window has passed.
+    ``shared_values``: a key's first ``value_dim`` entries are its value; no values are stored."""
     kind: str = "none"
     kv_heads: int = 0
     head_dim: int = 0
@@ -80,14 +81,20 @@ class CacheNeed:
     value_dim: int = 0
     states: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
     keep_first: int = 0
+    shared_values: bool = False
 
     @property
     def v_dim(self) -> int:
         return self.value_dim or self.head_dim
 
+    @property
+    def stored_v_dim(self) -> int:
+        """Entries a page holds per value (0 where values are read out of the keys)."""
+        return 0 if self.shared_values else self.v_dim
+
     def group_key(self):
         return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape, self.state_dtype,
-                self.value_dim, self.states, self.keep_first)
+                self.value_dim, self.states, self.keep_first, self.shared_values)
 
     def merged(self, other: "CacheNeed") -> "CacheNeed":
         """The need of a cache entry that ``self`` and ``other`` both read: everything either of them

@@ -1,7 +1,11 @@
-"""Dense feed-forward with one hidden layer: W_down act(W_up h), act the tanh form of gelu,
-gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), worked out in float32."""
+"""Dense feed-forwards with one hidden layer, W_down act(W_up h), the activation worked out in float32.
+
+``gelu_mlp``: the tanh form of gelu, gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+``xielu_mlp``: xIELU with two learned numbers (p, q) per layer: for z > 0, softplus(p) z^2 + z / 2; for z <= 0,
+(1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2."""
 from __future__ import annotations
 
+import math
 from typing import Dict
 
 from .base import Part, PartSpec, Runtime, TensorSpec, register_part
@@ -24,3 +28,21 @@ class GeluMLP(Part):
     def forward(self, x):
         ops = self.rt.ops
         return ops.linear(ops.gelu_tanh(ops.linear(x, self.w_up)), self.w_down)
+
+
+@register_part("ffn", "xielu_mlp")
+class XieluMLP(GeluMLP):
+    """params: ``hidden``, ``inter``.  Tensors: ``up`` [inter, hidden], ``down`` [hidden, inter], ``act`` [2] = (p, q)."""
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {**super().tensor_specs(), "act": TensorSpec((2,), "uniform", lo=-1.0, hi=1.0)}
+
+    def load(self, t) -> None:
+        super().load(t)
+        softplus = lambda v: max(v, 0.0) + math.log1p(math.exp(-abs(v)))
+        p, q = (float(v) for v in t["act"].to("cpu", dtype=__import__("torch").float64))
+        self.pos_factor, self.neg_factor = softplus(p), 0.5 + softplus(q)     # worked out once, in float64
+
+    def forward(self, x):
+        ops = self.rt.ops
+        return ops.linear(ops.xielu(ops.linear(x, self.w_up), self.pos_factor, self.neg_factor), self.w_down)

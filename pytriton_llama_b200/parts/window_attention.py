@@ -8,6 +8,11 @@ of their own size.  The nested ``position`` part then turns neighbouring pairs o
 or j < ``keep_first`` (``window`` 0: every j <= i); a kept key was rotated by its own position like any other.
 score = (q . k) * scale, softmax, heads of ``value_dim`` concatenated, W_o.
 
+Two options change the scores.  ``sink``: the softmax has one more term of score 0 in its denominator
+(a key that every query sees and that has no value), p_j = exp(s_j) / (1 + sum exp(s_j)).
+``q_temp`` = {coef, every}: the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1);
+the factor is applied to the float32 scores, which is the same thing.
+
 With ``own_kv`` False the layer has no key and value tensors: it attends, with its own queries and
 its own window, over the cache entry that another layer writes (``RunEntry.write`` False).
 """
@@ -64,7 +69,7 @@ class RotaryPairs(Part):
 @register_part("mixer", "window_attention")
 class WindowAttention(Part):
     """params: ``hidden``, ``heads``, ``kv_heads``, ``head_dim``, ``value_dim``, ``scale``, ``window``, ``keep_first``,
-    ``qk_norm_eps``, ``own_kv``.  Nested part ``position``.  Tensors: ``q`` [heads*d, hidden], ``o`` [hidden,
+    ``qk_norm_eps``, ``own_kv``, ``sink``, ``q_temp``.  Nested part ``position`` (none: no encoding).  Tensors: ``q`` [heads*d, hidden], ``o`` [hidden,
     heads*value_dim], ``q.norm`` [heads*d]; with ``own_kv`` ``k`` [kv_heads*d, hidden], ``v`` [kv_heads*value_dim,
     hidden], ``k.norm`` [kv_heads*d]."""
 
@@ -77,6 +82,9 @@ class WindowAttention(Part):
         self.window, self.keep_first = int(p.get("window") or 0), int(p.get("keep_first") or 0)
         self.qk_norm_eps = float(p.get("qk_norm_eps") or 0.0)
         self.own_kv = bool(p.get("own_kv", True))
+        self.sink = bool(p.get("sink", False))
+        temp = p.get("q_temp") or {}
+        self.temp_coef, self.temp_every = float(temp.get("coef", 0.0)), int(temp.get("every", 1))
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.heads} query heads are no multiple of {self.kv_heads} kv heads")
         self.position = build_part("position", spec.parts["position"], runtime) if "position" in spec.parts else None
@@ -120,5 +128,6 @@ class WindowAttention(Part):
                                  g.slots if self.own_kv else None, cache.kv if self.own_kv else None, g.page_size)
         o = ops.window_attention(proj, cache.kv, g.block_table, ctx.tok_req, ctx.positions, self.heads, self.kv_heads, self.d,
                                  self.dv, g.page_size, self.scale, window=self.window, keep_first=self.keep_first,
-                                 splits=ctx.attn_splits, hints=ctx)
+                                 splits=ctx.attn_splits, hints=ctx, sink=self.sink, temp_coef=self.temp_coef,
+                                 temp_every=self.temp_every)
         return ops.linear(o, self.w_o)

@@ -264,12 +264,13 @@ class TorchOps:
             S_all[slot] = S.float()
         return o.reshape(T, H * dv).float()
 
-    def gated_head_norm(self, o, weight, eps, gate, gate_column, H, dv, out, column, scale):
+    def gated_head_norm(self, o, weight, eps, gate, gate_column, H, dv, out, column, scale, gate_kind="silu", weight_per_head=False):
         T = o.shape[0]
         x = o.double().view(T, H, dv)
-        x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * weight.double()
+        x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * (weight.double().view(H, dv) if weight_per_head else weight.double())
         g = gate[:, gate_column:gate_column + H * dv].double()
-        out[:, column:column + H * dv] = (x.reshape(T, H * dv) * g * torch.sigmoid(g) * scale).to(out.dtype)
+        g = torch.sigmoid(g) if gate_kind == "sigmoid" else g * torch.sigmoid(g)
+        out[:, column:column + H * dv] = (x.reshape(T, H * dv) * g * scale).to(out.dtype)
 
     def clamped_glu(self, gu, bias, limit, alpha, up_shift):
         inter = gu.shape[1] // 2
@@ -333,7 +334,7 @@ class TorchOps:
                 vp[:, off] = proj[t, (H + G) * d:(H + G) * d + G * dv].view(G, dv)
 
     def window_attention(self, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window=0, keep_first=0,
-                         splits=1, hints=None):
+                         splits=1, hints=None, sink=False, temp_coef=0.0, temp_every=1, shared_values=False):
         T = q.shape[0]
         out = torch.zeros((T, H * dv), dtype=torch.float64)
         group = H // G
@@ -346,13 +347,24 @@ class TorchOps:
             for j in keys:
                 page = int(block_table[r, j // page_size])
                 assert page >= 0, "attention reads a page that was given back"
-                kp, vp = self._page_views(cache, page, G, page_size, d, dv)
+                if shared_values:           # a page holds keys only; a key's first dv entries are its value
+                    kp = cache[page].view(G, page_size, d)
+                    vp = kp[..., :dv]
+                else:
+                    kp, vp = self._page_views(cache, page, G, page_size, d, dv)
                 ks.append(kp[:, j % page_size].double())
                 vs.append(vp[:, j % page_size].double())
             k, v = torch.stack(ks), torch.stack(vs)
             qt = q[t, :H * d].double().view(H, d)
+            temp = 1.0 + temp_coef * math.log((p + 1) // temp_every + 1.0) if temp_coef else 1.0
             for h in range(H):
-                w = torch.softmax((k[:, h // group] @ qt[h]) * scale, 0)
+                sc = (k[:, h // group] @ qt[h]) * scale * temp
+                if sink:
+                    m = max(float(sc.max()), 0.0)
+                    ex = torch.exp(sc - m)
+                    w = ex / (ex.sum() + math.exp(-m))
+                else:
+                    w = torch.softmax(sc, 0)
                 out[t, h * dv:(h + 1) * dv] = w @ v[:, h // group]
         return out.to(q.dtype)
 
@@ -392,3 +404,88 @@ class TorchOps:
         if shared is not None:
             out += shared.double()
         return out.float()
+
+    # ------------------------------------------------------------------ operators of the Sogalix parts
+    def add_layernorm(self, x, residual, weight, bias, eps, rows=None, dtype=None, add_bias=None, keep_sum=True):
+        dtype = dtype or x.dtype
+        s = None
+        if residual is not None:
+            s = residual.double()
+        if x is not None:
+            s = x.double() if s is None else s + x.double()
+        if add_bias is not None:
+            s = s + add_bias.double()
+        if rows is not None:
+            s = s[rows.long()]
+        mu = s.mean(-1, keepdim=True)
+        var = ((s - mu) ** 2).mean(-1, keepdim=True)
+        y = ((s - mu) / torch.sqrt(var + eps) * weight.double() + bias.double()).to(dtype)
+        if rows is not None or not keep_sum:
+            return y, None
+        if residual is not None:
+            residual.copy_(s.float())
+            return y, residual
+        return y, s.float()
+
+    def lowrank_tanh_linear(self, aw, column, w2):
+        return (torch.tanh(aw[:, column:].double()) @ w2.double().T).float()
+
+    def general_delta_scan(self, proj, aw, a_bias, z, w_bias, decay_limit, S_all, ctx, H, d, unit_eps):
+        T, n = proj.shape[0], H * d
+        x = proj.double()
+        r, k, v = (x[:, i * n:(i + 1) * n].view(T, H, d) for i in range(3))
+        a = torch.sigmoid(aw[:, :n].double() + a_bias.double()).view(T, H, d)
+        w = torch.exp(-decay_limit * torch.sigmoid(z.double() + w_bias.double())).view(T, H, d)
+        u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+        o = torch.zeros((T, H, d), dtype=torch.float64)
+        for lo, hi, slot, pos0 in self._requests(ctx):
+            S = S_all[slot].double() if pos0 > 0 else torch.zeros((H, d, d), dtype=torch.float64)
+            for t in range(lo, hi):
+                uS = torch.einsum("hc,hce->he", u[t], S)
+                S = w[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * uS[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
+                o[t] = torch.einsum("hce,hc->he", S, r[t])
+            S_all[slot] = S.float()
+        return o.reshape(T, n).float()
+
+    def xielu(self, x, pos_factor, neg_factor):
+        z = x.double()
+        neg = z.clamp(max=0)
+        return torch.where(z > 0, pos_factor * z * z + 0.5 * z, neg_factor * (torch.expm1(neg) - neg) + 0.5 * z).to(x.dtype)
+
+    def latent_norm_store(self, proj, Q, q_norm, R, kv_norm, n, eps, positions, freq, dims, slots, cache, page_size):
+        x = proj.double()
+        unit = lambda t: t / torch.sqrt((t * t).mean(-1, keepdim=True) + eps)
+        cq = (unit(x[:, :Q]) * q_norm.double()).to(proj.dtype)
+        if R:
+            c = unit(x[:, Q:Q + R]) * kv_norm.double()
+            kr = x[:, Q + R:Q + R + n].clone()
+            ang = positions.double()[:, None] * freq.double()[None, :dims // 2]
+            a, b = kr[:, 0:dims:2].clone(), kr[:, 1:dims:2].clone()
+            kr[:, 0:dims:2] = a * ang.cos() - b * ang.sin()
+            kr[:, 1:dims:2] = b * ang.cos() + a * ang.sin()
+            row = torch.cat([c, kr], dim=1).to(cache.dtype)
+            for t in range(proj.shape[0]):
+                sl = int(slots[t])
+                if sl >= 0:
+                    page, off = divmod(sl, page_size)
+                    cache[page].view(page_size, R + n)[off] = row[t]
+        return cq
+
+    def head_linear(self, x, x_ld, x_col, w, out, out_ld, out_col, H, gate=None, gate_column=0):
+        T = x.shape[0]
+        n_out, n_in = w.shape[1], w.shape[2]
+        xs = x.double().view(T, H, x_ld)[:, :, x_col:x_col + n_in]
+        y = torch.einsum("thi,hoi->tho", xs, w.double())
+        if gate is not None:
+            y = y * torch.sigmoid(gate[:, gate_column:gate_column + H].double())[:, :, None]
+        out.view(T, H, out_ld)[:, :, out_col:out_col + n_out] = y.to(out.dtype)
+
+    def rotate_head_part(self, x, x_ld, x_col, out, out_ld, out_col, H, n, positions, freq, dims):
+        T = x.shape[0]
+        part = x.double().view(T, H, x_ld)[:, :, x_col:x_col + n].clone()
+        ang = positions.double()[:, None] * freq.double()[None, :dims // 2]
+        c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        a, b = part[..., 0:dims:2].clone(), part[..., 1:dims:2].clone()
+        part[..., 0:dims:2] = a * c - b * s
+        part[..., 1:dims:2] = b * c + a * s
+        out.view(T, H, out_ld)[:, :, out_col:out_col + n] = part.to(out.dtype)
