@@ -1,6 +1,9 @@
 // out[M, N] (+)= A[M, K] * W[N, K]^T on the CUDA cores in float32: the true 32-bit matrix product
 // of the float32 path (no tensor-core mode that drops mantissa bits), and a library-free check for
 // the bfloat16 tensor-core kernels.  Any M, N, K; both operands are K-contiguous.
+// A launch may hold several products of one shape (blockIdx.z = b): operand and result pointers move on by
+// batch_a, batch_w, batch_o elements per b (the heads of an activation [M, heads * x] against weights
+// [heads, N, K]); with `gate` the result of row m of product b is multiplied by sigmoid(gate[m * gate_ld + b]).
 //
 // Summation order, the same for every tile shape, so that a row's result does not depend on how
 // many rows the call has (a prompt portion and a single decoded token give the same bits):
@@ -26,12 +29,16 @@ __device__ __forceinline__ void kahan_add(float& sum, float& comp, float chunk) 
 template <typename TI, typename TO, int BM, int BN, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(TO* __restrict__ out, const TI* __restrict__ A, const TI* __restrict__ W,
-                 int M, int N, int K, int lda, int ldw, int ldo, int accumulate, int vec_ok) {
+                 int M, int N, int K, int lda, int ldw, int ldo, int accumulate, int vec_ok,
+                 long long batch_a, long long batch_w, long long batch_o, const TI* __restrict__ gate, int gate_ld) {
   constexpr int BK = kSimtChunk;
   constexpr int THREADS = (BM / TM) * (BN / TN);
   static_assert(TM % 4 == 0 || TM == 2 || TM == 1, "rows per thread");
   pdl_wait();
   pdl_launch_dependents();
+  A += (size_t)blockIdx.z * batch_a;
+  W += (size_t)blockIdx.z * batch_w;
+  out += (size_t)blockIdx.z * batch_o;
   __shared__ __align__(16) float As[BK][BM + 4];
   __shared__ __align__(16) float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -103,12 +110,13 @@ gemm_simt_kernel(TO* __restrict__ out, const TI* __restrict__ A, const TI* __res
   for (int i = 0; i < TM; ++i) {
     const int gm = m0 + ty * TM + i;
     if (gm >= M) continue;
+    const float row_gate = gate ? 1.0f / (1.0f + expf(-to_f32(gate[(size_t)gm * gate_ld + blockIdx.z]))) : 1.0f;
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
       const int gn = n0 + tx * TN + j;
       if (gn >= N) continue;
       TO* o = out + (size_t)gm * ldo + gn;
-      float v = sum[i][j];
+      float v = sum[i][j] * row_gate;
       if (accumulate) v += to_f32(*o);
       *o = from_f32<TO>(v);
     }
@@ -117,23 +125,29 @@ gemm_simt_kernel(TO* __restrict__ out, const TI* __restrict__ A, const TI* __res
 
 template <typename TI, typename TO>
 int gemm_simt(void* out, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldo,
-              int accumulate, void* stream) {
+              int accumulate, void* stream, int batch = 1, long long batch_a = 0, long long batch_w = 0, long long batch_o = 0,
+              const void* gate_v = nullptr, int gate_ld = 0) {
   PTL_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_simt: bad sizes M=%d N=%d K=%d", M, N, K);
   PTL_REQUIRE(lda >= K && ldw >= K && ldo >= N, "gemm_simt: pitches smaller than rows");
+  PTL_REQUIRE(batch >= 1 && batch <= 65535, "gemm_simt: %d products in one launch", batch);
   if (M == 0) return 0;
-  const int vec_ok = sizeof(TI) == 4 && K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && aligned16(A) && aligned16(W);
+  const TI* gate = (const TI*)gate_v;
+  const int vec_ok = sizeof(TI) == 4 && K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && aligned16(A) && aligned16(W) &&
+                     batch_a % 4 == 0 && batch_w % 4 == 0;
   if (M > 32) {
     constexpr int BM = 128, BN = 64, TM = 8, TN = 4;
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     PTL_REQUIRE(grid.y <= 65535, "gemm_simt: M=%d too large", M);
     return launch_kernel("gemm_simt", gemm_simt_kernel<TI, TO, BM, BN, TM, TN>, grid, dim3((BM / TM) * (BN / TN)), 0,
-                         as_stream(stream), (TO*)out, (const TI*)A, (const TI*)W, M, N, K, lda, ldw, ldo, accumulate, vec_ok);
+                         as_stream(stream), (TO*)out, (const TI*)A, (const TI*)W, M, N, K, lda, ldw, ldo, accumulate, vec_ok,
+                         batch_a, batch_w, batch_o, gate, gate_ld);
   } else {
     // few rows: narrow tiles so that the weight matrix is spread over many blocks
     constexpr int BM = 32, BN = 16, TM = 4, TN = 1;
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     return launch_kernel("gemm_simt", gemm_simt_kernel<TI, TO, BM, BN, TM, TN>, grid, dim3((BM / TM) * (BN / TN)), 0,
-                         as_stream(stream), (TO*)out, (const TI*)A, (const TI*)W, M, N, K, lda, ldw, ldo, accumulate, vec_ok);
+                         as_stream(stream), (TO*)out, (const TI*)A, (const TI*)W, M, N, K, lda, ldw, ldo, accumulate, vec_ok,
+                         batch_a, batch_w, batch_o, gate, gate_ld);
   }
 }
 
@@ -147,4 +161,16 @@ PTL_EXPORT int ptl_gemm_simt_bf16(void* out, const void* A, const void* W, int M
 }
 PTL_EXPORT int ptl_gemm_simt_bf16_f32out(void* out, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldo, int accumulate, void* stream) {
   return ptl::gemm_simt<__nv_bfloat16, float>(out, A, W, M, N, K, lda, ldw, ldo, accumulate, stream);
+}
+
+// The heads of an activation against per-head weights: for b < heads,
+//   out[m, b * batch_o + n] = sum_k A[m, b * batch_a + k] * W[b, n, k]   (times sigmoid(gate[m * gate_ld + b]) with a gate).
+PTL_EXPORT int ptl_head_linear_f32(void* out, const void* A, const void* W, int M, int N, int K, int lda, int ldo, int heads,
+                                   int batch_a, int batch_o, const void* gate, int gate_ld, void* stream) {
+  return ptl::gemm_simt<float, float>(out, A, W, M, N, K, lda, K, ldo, 0, stream, heads, batch_a, (long long)N * K, batch_o, gate, gate_ld);
+}
+PTL_EXPORT int ptl_head_linear_bf16(void* out, const void* A, const void* W, int M, int N, int K, int lda, int ldo, int heads,
+                                    int batch_a, int batch_o, const void* gate, int gate_ld, void* stream) {
+  return ptl::gemm_simt<__nv_bfloat16, __nv_bfloat16>(out, A, W, M, N, K, lda, K, ldo, 0, stream, heads, batch_a, (long long)N * K,
+                                                      batch_o, gate, gate_ld);
 }

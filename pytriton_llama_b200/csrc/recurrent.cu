@@ -385,12 +385,13 @@ gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, cons
 
 // ------------------------------------------------------------------ per-head norm with an output gate
 // out[t, column + h * dv + e] = o[t, h, e] * rsqrt(mean_e(o^2) + eps) * w[e] * silu(gate[t, gate_column + h * dv + e]) * scale.
+// With `sigmoid_gate` the gate passes a sigmoid instead of silu; with `weight_per_head` the weight is w[h * dv + e].
 // One warp per (token, head).
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_head_norm_kernel(T* __restrict__ out, int out_ld, int column, const float* __restrict__ o, const float* __restrict__ w,
                        float eps, const T* __restrict__ gate, int gate_ld, int gate_column, int tokens, int heads, int dv,
-                       float scale) {
+                       float scale, int sigmoid_gate, int weight_per_head) {
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -403,10 +404,12 @@ gated_head_norm_kernel(T* __restrict__ out, int out_ld, int column, const float*
   for (int e = lane; e < dv; e += 32) ss = fmaf(src[e], src[e], ss);
   ss = warp_sum(ss);
   const float rrms = 1.0f / sqrtf(ss / (float)dv + eps);
+  const float* wh = weight_per_head ? w + (size_t)h * dv : w;
 #pragma unroll 4
   for (int e = lane; e < dv; e += 32) {
     const float g = to_f32(gate[(size_t)t * gate_ld + gate_column + h * dv + e]);
-    out[(size_t)t * out_ld + column + h * dv + e] = from_f32<T>(src[e] * rrms * w[e] * silu_f32(g) * scale);
+    const float gated = sigmoid_gate ? 1.0f / (1.0f + expf(-g)) : silu_f32(g);
+    out[(size_t)t * out_ld + column + h * dv + e] = from_f32<T>(src[e] * rrms * wh[e] * gated * scale);
   }
 }
 
@@ -480,7 +483,7 @@ int gated_delta_rule(float* out, const void* qkv, const float* ba, const float* 
 
 template <typename T>
 int gated_head_norm(void* out, int out_ld, int column, const float* o, const float* w, float eps, const void* gate, int gate_ld,
-                    int gate_column, int tokens, int heads, int dv, float scale, void* stream) {
+                    int gate_column, int tokens, int heads, int dv, float scale, int sigmoid_gate, int weight_per_head, void* stream) {
   PTL_REQUIRE(tokens >= 0 && heads > 0 && dv > 0 && eps > 0.f && column >= 0 && column + heads * dv <= out_ld &&
               gate_column >= 0 && gate_column + heads * dv <= gate_ld, "gated_head_norm: bad sizes tokens=%d heads=%d dv=%d",
               tokens, heads, dv);
@@ -488,7 +491,7 @@ int gated_head_norm(void* out, int out_ld, int column, const float* o, const flo
   const size_t items = (size_t)tokens * heads;
   return launch_kernel("gated_head_norm", gated_head_norm_kernel<T>, dim3((unsigned)((items + 7) / 8)), dim3(256), 0,
                        as_stream(stream), (T*)out, out_ld, column, o, w, eps, (const T*)gate, gate_ld, gate_column, tokens, heads,
-                       dv, scale);
+                       dv, scale, sigmoid_gate, weight_per_head);
 }
 
 }  // namespace ptl
@@ -517,9 +520,9 @@ int gated_head_norm(void* out, int out_ld, int column, const float* o, const flo
   }                                                                                                                               \
   PTL_EXPORT int ptl_gated_head_norm##SUFFIX(void* out, int out_ld, int column, const float* o, const float* w, float eps,         \
                                              const void* gate, int gate_ld, int gate_column, int tokens, int heads, int dv,        \
-                                             float scale, void* stream) {                                                         \
+                                             float scale, int sigmoid_gate, int weight_per_head, void* stream) {                  \
     return ptl::gated_head_norm<TYPE>(out, out_ld, column, o, w, eps, gate, gate_ld, gate_column, tokens, heads, dv, scale,        \
-                                      stream);                                                                                    \
+                                      sigmoid_gate, weight_per_head, stream);                                                     \
   }
 PTL_RECURRENT(_f32, float)
 PTL_RECURRENT(_bf16, __nv_bfloat16)

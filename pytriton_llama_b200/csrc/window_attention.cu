@@ -19,6 +19,9 @@
 // (see attention_simt.cu).  The list may be split over blockIdx.z and merged by a second kernel.
 // The kernel works `tokens` rows, or the rows that `items` names (the single tokens of a step
 // whose longer portions another kernel takes); partial results are indexed by the row itself.
+// Options: `sink` adds one term of score 0 (and no value) to the softmax's denominator; `temp_coef` != 0
+// multiplies the scores of the query at position p by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1);
+// `shared_v`: pages hold keys only and the value of a key is its first dv entries.
 #include "common.cuh"
 
 namespace ptl {
@@ -219,7 +222,8 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
                         const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_table,
                         const int* __restrict__ tok_req, const int* __restrict__ positions, int q_stride, int out_stride,
                         int bt_stride, int H, int G, int d, int dv, int page_size, float scale, int window, int keep,
-                        int splits, int num_pages, int vec_ok, const int* __restrict__ items, int wide_ok) {
+                        int splits, int num_pages, int vec_ok, const int* __restrict__ items, int wide_ok, int shared_v,
+                        int sink, float temp_coef, int temp_every) {
   extern __shared__ float qs_all[];  // [warps][d]
   __shared__ float s_pr[kWaWarps][32];
   __shared__ unsigned long long s_vb[kWaWarps][32];
@@ -233,11 +237,12 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
   float* qs = qs_all + warp * d;
   const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
   constexpr bool kCompensated = sizeof(T) == 4;
+  const int r = tok_req[t];        // r < 0: a padding row; it sees no key and yields zeros
+  const int p = positions[t];
+  if (temp_coef != 0.f) scale *= fmaf(temp_coef, logf((float)((p + 1) / temp_every) + 1.0f), 1.0f);
   for (int i = lane; i < d; i += 32) qs[i] = kCompensated ? to_f32(qrow[i]) : to_f32(qrow[i]) * scale;
   __syncwarp();
 
-  const int r = tok_req[t];        // r < 0: a padding row; it sees no key and yields zeros
-  const int p = positions[t];
   const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int n_keep = min(keep, lo);                 // kept positions that the window has passed
   const int n_list = r < 0 ? 0 : n_keep + (p - lo + 1);
@@ -246,8 +251,9 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
   const int i_begin = split * chunk;
   const int i_end = min(i_begin + chunk, n_list);
   const int g = h / (H / G);
-  const size_t page_stride = (size_t)G * page_size * (d + dv);
-  const size_t v_plane = (size_t)G * page_size * d;
+  const size_t page_stride = (size_t)G * page_size * (d + (shared_v ? 0 : dv));
+  const size_t v_plane = shared_v ? 0 : (size_t)G * page_size * d;
+  const int v_row = shared_v ? d : dv;      // elements between the values of neighbouring keys
   const int* bt = block_table + (size_t)(r < 0 ? 0 : r) * bt_stride;
   constexpr int VN = Vec16<T>::N;
 
@@ -267,7 +273,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
     if (valid) {
       const size_t in_page = (size_t)g * page_size + key % page_size;
       const T* kp = cache + (size_t)page * page_stride + in_page * d;
-      vbase = (size_t)page * page_stride + v_plane + in_page * dv;
+      vbase = (size_t)page * page_stride + v_plane + in_page * v_row;
       float dot = 0.f, dot_lo = 0.f;
       if (vec_ok) {
         // four packets of the key row are requested together and used afterwards: a product right behind its load
@@ -380,6 +386,13 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
     for (int i = 0; i < kWaMaxPerLane; ++i) acc[i] = __fadd_rn(acc[i], acc_lo[i]);
   }
   if (splits == 1) {
+    if (sink) {            // the term of score 0 joins as a key would: the maximum may move to 0, and exp(0 - maximum) is added
+      const float m_all = fmaxf(m, 0.f);
+      const float a = expf(m - m_all);
+      l = fmaf(l, a, expf(-m_all));
+#pragma unroll
+      for (int i = 0; i < kWaMaxPerLane; ++i) acc[i] *= a;
+    }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     T* o = out + (size_t)t * out_stride + (size_t)h * dv;
 #pragma unroll
@@ -403,7 +416,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
 template <typename T>
 __global__ void __launch_bounds__(kWaWarps * 32)
 window_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                              int out_stride, int H, int dv, int splits, int tokens, const int* __restrict__ items) {
+                              int out_stride, int H, int dv, int splits, int tokens, const int* __restrict__ items, int sink) {
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -417,6 +430,7 @@ window_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ par
   float M = -INFINITY;
   for (int z = lane; z < splits; z += 32) M = fmaxf(M, part_ml[(idx0 + z) * 2]);
   M = warp_max(M);
+  if (sink) M = fmaxf(M, 0.f);
   float L = 0.f;
   float acc[kWaMaxPerLane];
 #pragma unroll
@@ -457,6 +471,7 @@ window_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ par
     }
   }
   L = warp_sum(L);
+  if (sink) L += expf(-M);
   const float inv = L > 0.f ? 1.0f / L : 0.f;
   T* o = out + (size_t)t * out_stride + (size_t)h * dv;
 #pragma unroll
@@ -470,8 +485,10 @@ template <typename T>
 int window_attention(void* out, const void* q, const void* cache, const int* block_table, const int* tok_req,
                      const int* positions, float* part_acc, float* part_ml, int tokens, int q_stride, int out_stride,
                      int bt_stride, int H, int G, int d, int dv, int page_size, float scale, int window, int keep, int splits,
-                     int num_pages, const int* items, void* stream) {
+                     int num_pages, const int* items, int shared_v, int sink, float temp_coef, int temp_every, void* stream) {
   PTL_REQUIRE(tokens >= 0 && H > 0 && G > 0 && page_size > 0 && d > 0, "window_attention: bad sizes");
+  PTL_REQUIRE(!shared_v || dv <= d, "window_attention: values of %d entries inside keys of %d", dv, d);
+  PTL_REQUIRE(temp_every >= 1, "window_attention: temp_every=%d", temp_every);
   PTL_REQUIRE(H % G == 0, "window_attention: %d query heads are no multiple of %d kv heads", H, G);
   PTL_REQUIRE(dv >= 1 && dv <= 32 * kWaMaxPerLane, "window_attention: value heads of %d, at most %d", dv, 32 * kWaMaxPerLane);
   PTL_REQUIRE(d <= 2048, "window_attention: head size %d", d);
@@ -480,24 +497,26 @@ int window_attention(void* out, const void* q, const void* cache, const int* blo
   PTL_REQUIRE(window >= 0 && keep >= 0 && num_pages > 0, "window_attention: window and kept positions must be >= 0");
   if (tokens == 0) return 0;
   constexpr int VN = Vec16<T>::N;
-  const int vec_ok = aligned16(cache) && d % VN == 0 && ((size_t)page_size * G * (d + dv)) % VN == 0 &&
+  const int dv_stored = shared_v ? 0 : dv;
+  const int vec_ok = aligned16(cache) && d % VN == 0 && ((size_t)page_size * G * (d + dv_stored)) % VN == 0 &&
                      ((size_t)G * page_size * d) % VN == 0;
   // bfloat16 value heads of 64 or 128 whose rows start on 8-byte boundaries: a lane fetches 2 or 4 neighbours at once
   int wide_ok = 0;
   if (sizeof(T) == 2 && (dv == 64 || dv == 128) && aligned16(cache) && ((size_t)G * page_size * d) % 4 == 0 &&
-      ((size_t)page_size * G * (d + dv)) % 4 == 0)
+      ((size_t)page_size * G * (d + dv_stored)) % 4 == 0 && (!shared_v || d % 4 == 0))
     wide_ok = dv / 32;
   dim3 grid(tokens, (H + kWaWarps - 1) / kWaWarps, splits);
   const size_t smem = (size_t)kWaWarps * d * sizeof(float);
   int rc = launch_kernel("window_attention", window_attention_kernel<T>, grid, dim3(kWaWarps * 32), smem, as_stream(stream),
                          (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req, positions, q_stride,
-                         out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages, vec_ok, items, wide_ok);
+                         out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages, vec_ok, items, wide_ok,
+                         shared_v, sink, temp_coef, temp_every);
   if (rc) return rc;
   if (splits > 1) {
     const long long pairs = (long long)tokens * H;
     rc = launch_kernel("window_attention_merge", window_attention_merge_kernel<T>,
                        dim3((unsigned)((pairs + kWaWarps - 1) / kWaWarps)), dim3(kWaWarps * 32), 0, as_stream(stream), (T*)out,
-                       (const float*)part_acc, (const float*)part_ml, out_stride, H, dv, splits, tokens, items);
+                       (const float*)part_acc, (const float*)part_ml, out_stride, H, dv, splits, tokens, items, sink);
   }
   return rc;
 }
@@ -516,10 +535,11 @@ int window_attention(void* out, const void* q, const void* cache, const int* blo
                                               const int* tok_req, const int* positions, float* part_acc, float* part_ml,           \
                                               int tokens, int q_stride, int out_stride, int bt_stride, int H, int G, int d, int dv, \
                                               int page_size, float scale, int window, int keep, int splits, int num_pages,         \
-                                              const int* items, void* stream) {                                                                      \
+                                              const int* items, int shared_v, int sink, float temp_coef, int temp_every,           \
+                                              void* stream) {                                                                      \
     return ptl::window_attention<TYPE>(out, q, cache, block_table, tok_req, positions, part_acc, part_ml, tokens, q_stride,        \
                                        out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages,      \
-                                       items, stream);                                                                                    \
+                                       items, shared_v, sink, temp_coef, temp_every, stream);                                      \
   }
 PTL_WINDOW_ATTENTION(_f32, float)
 PTL_WINDOW_ATTENTION(_bf16, __nv_bfloat16)

@@ -38,7 +38,8 @@ _SIGNATURES = {
                            _c_int, _ptr],
     "ptl_gated_delta_rule": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f,
                              _c_f, _ptr],
-    "ptl_gated_head_norm": [_ptr, _c_int, _c_int, _ptr, _ptr, _c_f, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr],
+    "ptl_gated_head_norm": [_ptr, _c_int, _c_int, _ptr, _ptr, _c_f, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int,
+                            _ptr],
     "ptl_kv_write_normed": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_f, _ptr],
     "ptl_chunk_attention": [_ptr, _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int,
                             _c_int, _c_int, _c_int, _c_f, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr],
@@ -47,7 +48,15 @@ _SIGNATURES = {
     "ptl_qk_norm_rotate_store": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _c_int, _c_f, _ptr,
                                  _ptr, _c_int, _c_ll, _ptr],
     "ptl_window_attention": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                             _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr],
+                             _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _c_f, _c_int, _ptr],
+    "ptl_add_layernorm": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _c_int, _ptr],
+    "ptl_xielu": [_ptr, _ptr, _c_ll, _c_f, _c_f, _ptr],
+    "ptl_general_delta_scan": [_ptr, _ptr, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _c_f, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int,
+                               _c_int, _c_f, _ptr],
+    "ptl_latent_norm_store": [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr, _c_int, _c_f, _ptr, _ptr, _c_int, _ptr, _ptr,
+                              _c_ll, _ptr],
+    "ptl_rotate_head_part": [_ptr, _c_int, _c_int, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr],
+    "ptl_head_linear": [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr],
     "ptl_gla_scan": [_ptr, _ptr, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr],
     "ptl_moe_gather": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr],
     "ptl_moe_grouped": [_ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr],
@@ -160,6 +169,8 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_moe_wide_rows.restype = _c_int
     lib.ptl_moe_grouped_wide_bf16.argtypes = [_ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr]
     lib.ptl_moe_grouped_wide_bf16.restype = _c_int
+    lib.ptl_lowrank_tanh_linear.argtypes = [_ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr]
+    lib.ptl_lowrank_tanh_linear.restype = _c_int
     lib.ptl_last_error.restype = ctypes.c_char_p
     lib.ptl_set_dependent_launch.argtypes = [_c_int]
     lib.ptl_get_dependent_launch.restype = _c_int
@@ -261,6 +272,8 @@ class CudaOps:
         "sample": "sampling", "token_logprobs": "sampling",
         "stream_mix_norm": "norm", "gelu_tanh": "elementwise", "qk_norm_rotate_store": "rope", "window_attention": "attention",
         "gla_scan": "recurrent", "routed_experts": "experts",
+        "add_layernorm": "norm", "xielu": "elementwise", "lowrank_tanh_linear": "recurrent", "general_delta_scan": "recurrent",
+        "latent_norm_store": "rope", "rotate_head_part": "rope", "head_linear": "product",
     }
 
     def enable_timing(self) -> None:
@@ -950,15 +963,19 @@ class CudaOps:
         return out
 
     def gated_head_norm(self, o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, gate_column: int, H: int,
-                        dv: int, out: torch.Tensor, column: int, scale: float) -> None:
-        """out[:, column + h*dv + e] = o[:, h, e] / rms_e(o[:, h]) * weight[e] * silu(gate[:, gate_column + h*dv + e]) * scale."""
+                        dv: int, out: torch.Tensor, column: int, scale: float, gate_kind: str = "silu",
+                        weight_per_head: bool = False) -> None:
+        """out[:, column + h*dv + e] = o[:, h, e] / rms_e(o[:, h]) * weight[e] * silu(gate[:, gate_column + h*dv + e]) * scale.
+        ``gate_kind`` "sigmoid": the gate passes a sigmoid instead; ``weight_per_head``: the weight is [H*dv]."""
+        if gate_kind not in ("silu", "sigmoid") or weight.numel() != (H * dv if weight_per_head else dv):
+            raise KernelError("gated_head_norm: unknown gate or a weight of the wrong size")
         self._want(o, "o", torch.float32)
         self._want(weight, "norm weight", torch.float32)
         self._want(gate, "gate")
         self._want(out, "out", gate.dtype)
         fn = getattr(self.lib, "ptl_gated_head_norm" + _suffix(gate.dtype))
         self._check(fn(_p(out), out.shape[1], int(column), _p(o), _p(weight), float(eps), _p(gate), gate.shape[1], int(gate_column),
-                       o.shape[0], H, dv, float(scale), self._stream()))
+                       o.shape[0], H, dv, float(scale), int(gate_kind == "sigmoid"), int(weight_per_head), self._stream()))
 
     def kv_write_normed(self, qkv: torch.Tensor, bias: Optional[torch.Tensor], slots: torch.Tensor, cache: torch.Tensor, H: int,
                         G: int, d: int, dv: int, page_size: int, eps: float) -> None:
@@ -1070,17 +1087,28 @@ class CudaOps:
 
     def window_attention(self, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor,
                          positions: torch.Tensor, H: int, G: int, d: int, dv: int, page_size: int, scale: float, window: int = 0,
-                         keep_first: int = 0, splits: int = 1, hints=None) -> torch.Tensor:
+                         keep_first: int = 0, splits: int = 1, hints=None, sink: bool = False, temp_coef: float = 0.0,
+                         temp_every: int = 1, shared_values: bool = False) -> torch.Tensor:
         """Softmax attention of every token over the keys j <= p of its request with p - j < window or j < keep_first
-        (window 0: all); q is [T, >= H*d], the result [T, H*dv]."""
+        (window 0: all); q is [T, >= H*d], the result [T, H*dv].  ``sink``: one more term of score 0 in the
+        denominator; ``temp_coef``: scores of the query at position p times 1 + temp_coef * ln(floor((p + 1) /
+        temp_every) + 1); ``shared_values``: the cache's pages hold keys only and a key's first dv entries are its value."""
         self._want(q, "q")
         self._want(cache, "cache", q.dtype)
         for name, t in (("block_table", block_table), ("tok_req", tok_req), ("positions", positions)):
             self._want(t, name, torch.int32)
-        if cache[0].numel() != G * page_size * (d + dv):
+        if cache[0].numel() != G * page_size * (d + (0 if shared_values else dv)):
             raise KernelError("window_attention: the cache's pages do not fit the heads")
         tokens = q.shape[0]
         out = self.empty((tokens, H * dv), q.dtype)
+        options = (int(bool(shared_values)), int(bool(sink)), float(temp_coef), int(temp_every))
+        if options != (0, 0, 0.0, int(temp_every)):
+            longest = getattr(hints, "max_ctx_len", 0) or block_table.shape[1] * page_size
+            if window:
+                longest = min(longest, window + keep_first)
+            self._window_attention_simt(out, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window,
+                                        keep_first, self._window_splits(tokens, H, longest), None, options)
+            return out
         if (q.dtype == torch.bfloat16 and d == dv and d in (64, 128) and self._work(hints, "prefill_tiles") is not None
                 and self._work(hints, "decode_items") is not None and os.environ.get("PTL_WINDOW_TC", "1") != "0"):
             if self._window_attention_tensor_cores(out, q, cache, block_table, tok_req, positions, H, G, d, page_size, scale,
@@ -1100,8 +1128,9 @@ class CudaOps:
         return int(max(1, min(longest // 64, (self._sm_count * 16) // warps, 64)))
 
     def _window_attention_simt(self, out, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window,
-                               keep_first, splits, rows) -> None:
-        """``rows``: None for every token row, else (int32 row indices or None for 0..n-1, n)."""
+                               keep_first, splits, rows, options=(0, 0, 0.0, 1)) -> None:
+        """``rows``: None for every token row, else (int32 row indices or None for 0..n-1, n).  ``options``: (values
+        inside the keys, sink term, temperature coefficient, temperature step)."""
         tokens = q.shape[0]
         items, n_rows = (None, tokens) if rows is None else rows
         part_acc = part_ml = None
@@ -1111,7 +1140,8 @@ class CudaOps:
         fn = getattr(self.lib, "ptl_window_attention" + _suffix(q.dtype))
         self._check(fn(_p(out), _p(q), _p(cache), _p(block_table), _p(tok_req), _p(positions), _p(part_acc), _p(part_ml), n_rows,
                        q.shape[1], out.shape[1], block_table.shape[1], H, G, d, dv, page_size, float(scale), int(window),
-                       int(keep_first), int(splits), cache.shape[0], _p(items), self._stream()), kernels=2 if splits > 1 else 1)
+                       int(keep_first), int(splits), cache.shape[0], _p(items), *options, self._stream()),
+                    kernels=2 if splits > 1 else 1)
 
     def _window_attention_tensor_cores(self, out, q, cache, block_table, tok_req, positions, H, G, d, page_size, scale, window,
                                        keep_first, hints) -> bool:
@@ -1149,6 +1179,141 @@ class CudaOps:
         self._check(fn(_p(out), _p(proj), proj.shape[1], _p(z), _p(bias), float(inv_tau), _p(state), _p(ctx.q_start), _p(ctx.positions),
                        _p(ctx.state_slot), ctx.num_requests, H, d, dv, float(q_scale), self._stream()))
         return out
+
+    # ------------------------------------------------------------------ operators of the Sogalix parts
+    def add_layernorm(self, x: Optional[torch.Tensor], residual: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor,
+                      eps: float, rows: Optional[torch.Tensor] = None, dtype: Optional[torch.dtype] = None,
+                      add_bias: Optional[torch.Tensor] = None, keep_sum: bool = True):
+        """y = layernorm(residual + x (+ add_bias)) * weight + bias, the sum kept as the new float32 residual
+        (updated in place; created when ``residual`` is None, unless ``keep_sum`` is False).  With ``rows`` (int32
+        indices) only those rows are normed and no residual is written.  ``dtype``: y's element type; float32
+        from a bfloat16 ``x`` is allowed."""
+        src = x if x is not None else residual
+        hidden = src.shape[-1]
+        dtype = dtype or (x.dtype if x is not None else None)
+        if dtype is None:
+            raise KernelError("add_layernorm: give dtype when there is no x")
+        self._want(weight, "norm weight", torch.float32)
+        self._want(bias, "norm bias", torch.float32)
+        if x is not None:
+            self._want(x, "x")
+            if dtype not in (x.dtype, torch.float32):
+                raise KernelError("add_layernorm: y is of x's element type or float32")
+        if residual is not None:
+            self._want(residual, "residual", torch.float32)
+        if add_bias is not None:
+            self._want(add_bias, "add_bias", torch.float32)
+        if rows is not None:
+            self._want(rows, "rows", torch.int32)
+            n_out, res_out = rows.shape[0], None
+        else:
+            n_out = src.shape[0]
+            res_out = residual if residual is not None else (self.empty((n_out, hidden), torch.float32) if keep_sum else None)
+        y = self.empty((n_out, hidden), dtype)
+        x_type = x.dtype if x is not None else dtype
+        fn = getattr(self.lib, "ptl_add_layernorm" + _suffix(x_type))
+        self._check(fn(_p(y), _p(res_out), _p(residual), _p(x), _p(add_bias), _p(weight), _p(bias), _p(rows), n_out, hidden,
+                       float(eps), int(dtype == torch.float32 and x_type != torch.float32), self._stream()))
+        return y, res_out
+
+    def xielu(self, x: torch.Tensor, pos_factor: float, neg_factor: float) -> torch.Tensor:
+        """z > 0: pos_factor z^2 + z/2;  z <= 0: neg_factor (exp(z) - 1 - z) + z/2; float32 inside."""
+        self._want(x, "x")
+        out = torch.empty_like(x)
+        fn = getattr(self.lib, "ptl_xielu" + _suffix(x.dtype))
+        self._check(fn(_p(out), _p(x), x.numel(), float(pos_factor), float(neg_factor), self._stream()))
+        return out
+
+    def lowrank_tanh_linear(self, x: torch.Tensor, column: int, w2: torch.Tensor) -> torch.Tensor:
+        """tanh(x[:, column:column + rank]) @ w2[n, rank]^T, float32 [T, n]."""
+        self._want(x, "x", torch.float32)
+        self._want(w2, "w2", torch.float32)
+        n, rank = w2.shape
+        if column + rank != x.shape[1]:
+            raise KernelError("lowrank_tanh_linear: the inner inputs are the last columns of x")
+        z = self.empty((x.shape[0], n), torch.float32)
+        self._check(self.lib.ptl_lowrank_tanh_linear(_p(z), _p(x), x.shape[0], x.shape[1], int(column), rank, _p(w2), n,
+                                                     self._stream()))
+        return z
+
+    def general_delta_scan(self, proj: torch.Tensor, aw: torch.Tensor, a_bias: torch.Tensor, z: torch.Tensor, w_bias: torch.Tensor,
+                           decay_limit: float, state: torch.Tensor, ctx, H: int, d: int, unit_eps: float) -> torch.Tensor:
+        """The recurrence of ``parts/general_delta.py``: proj [T, r | k | v | ...]; aw float32 whose first H*d columns are
+        the removal rate's argument before its bias; z float32 [T, H*d], the decay's argument before its bias; state
+        float32 [slots, H, d, d]; returns the heads' read-outs, float32 [T, H*d]."""
+        self._want(proj, "proj")
+        for name, t in (("aw", aw), ("a_bias", a_bias), ("z", z), ("w_bias", w_bias), ("state", state)):
+            self._want(t, name, torch.float32)
+        n = H * d
+        if proj.shape[1] < 3 * n or aw.shape[1] < n or z.shape[1] != n or a_bias.numel() != n or w_bias.numel() != n or \
+                tuple(state.shape[1:]) != (H, d, d):
+            raise KernelError("general_delta_scan: shapes do not fit")
+        out = self.empty((proj.shape[0], n), torch.float32)
+        fn = getattr(self.lib, "ptl_general_delta_scan" + _suffix(proj.dtype))
+        self._check(fn(_p(out), _p(proj), proj.shape[1], _p(aw), aw.shape[1], _p(a_bias), _p(z), _p(w_bias), float(decay_limit),
+                       _p(state), _p(ctx.q_start), _p(ctx.positions), _p(ctx.state_slot), ctx.num_requests, H, d, float(unit_eps),
+                       self._stream()))
+        return out
+
+    def latent_norm_store(self, proj: torch.Tensor, Q: int, q_norm: torch.Tensor, R: int, kv_norm: Optional[torch.Tensor], n: int,
+                          eps: float, positions: torch.Tensor, freq: Optional[torch.Tensor], dims: int,
+                          slots: Optional[torch.Tensor], cache: Optional[torch.Tensor], page_size: int) -> torch.Tensor:
+        """On proj [T, q latent (Q) | kv latent (R) | rotated key part (n) | ...]: returns the RMS-normed q latent
+        [T, Q]; with R > 0 the normed kv latent and the key part, its pairs (2i, 2i+1), i < dims/2, turned by
+        position * freq[i], go to the tokens' slots of a cache whose pages hold keys of R + n entries only."""
+        self._want(proj, "proj")
+        self._want(q_norm, "q norm", torch.float32)
+        self._want(positions, "positions", torch.int32)
+        num_slots = 0
+        if R:
+            self._want(kv_norm, "kv norm", torch.float32)
+            self._want(cache, "cache", proj.dtype)
+            self._want(slots, "slots", torch.int32)
+            if freq is not None:
+                self._want(freq, "freq", torch.float32)
+            if cache[0].numel() != page_size * (R + n) or (dims and (freq is None or freq.numel() < dims // 2)):
+                raise KernelError("latent_norm_store: the cache's pages or the frequencies do not fit")
+            num_slots = cache.shape[0] * page_size
+        out = self.empty((proj.shape[0], Q), proj.dtype)
+        fn = getattr(self.lib, "ptl_latent_norm_store" + _suffix(proj.dtype))
+        self._check(fn(_p(out), _p(proj), proj.shape[0], proj.shape[1], Q, _p(q_norm), R, _p(kv_norm) if R else None, n if R else 0,
+                       float(eps), _p(positions), _p(freq) if R else None, int(dims) if R else 0, _p(slots) if R else None,
+                       _p(cache) if R else None, num_slots, self._stream()))
+        return out
+
+    def head_linear(self, x: torch.Tensor, x_ld: int, x_col: int, w: torch.Tensor, out: torch.Tensor, out_ld: int, out_col: int,
+                    H: int, gate: Optional[torch.Tensor] = None, gate_column: int = 0) -> None:
+        """For every head h: out[:, h*out_ld + out_col + o] = sum_i x[:, h*x_ld + x_col + i] * w[h, o, i], with ``gate``
+        times sigmoid(gate[:, gate_column + h]).  x rows hold H heads of x_ld entries, out rows H heads of out_ld."""
+        self._want(x, "x")
+        self._want(w, "w", x.dtype)
+        self._want(out, "out", x.dtype)
+        n_out, n_in = w.shape[1], w.shape[2]
+        if w.shape[0] != H or x.shape[1] != H * x_ld or out.shape[1] != H * out_ld or x_col + n_in > x_ld or out_col + n_out > out_ld:
+            raise KernelError("head_linear: shapes do not fit")
+        gate_ptr = None
+        if gate is not None:
+            self._want(gate, "gate", x.dtype)
+            gate_ptr = gate.data_ptr() + gate_column * gate.element_size()
+        fn = getattr(self.lib, "ptl_head_linear" + _suffix(x.dtype))
+        self._check(fn(out.data_ptr() + out_col * out.element_size(), x.data_ptr() + x_col * x.element_size(), _p(w), x.shape[0],
+                       n_out, n_in, x.shape[1], out.shape[1], H, x_ld, out_ld, gate_ptr, gate.shape[1] if gate is not None else 0,
+                       self._stream()))
+
+    def rotate_head_part(self, x: torch.Tensor, x_ld: int, x_col: int, out: torch.Tensor, out_ld: int, out_col: int, H: int, n: int,
+                         positions: torch.Tensor, freq: Optional[torch.Tensor], dims: int) -> None:
+        """The n entries at x_col of every head of x go to out_col of the same head of out, their pairs (2i, 2i+1),
+        i < dims/2, turned by position * freq[i]."""
+        self._want(x, "x")
+        self._want(out, "out", x.dtype)
+        self._want(positions, "positions", torch.int32)
+        if freq is not None:
+            self._want(freq, "freq", torch.float32)
+        if x.shape[1] != H * x_ld or out.shape[1] != H * out_ld:
+            raise KernelError("rotate_head_part: shapes do not fit")
+        fn = getattr(self.lib, "ptl_rotate_head_part" + _suffix(x.dtype))
+        self._check(fn(_p(out), out_ld, out_col, _p(x), x_ld, x_col, x.shape[0], H, n, _p(positions), _p(freq),
+                       int(dims) if freq is not None else 0, self._stream()))
 
     moe_tensor_cores = os.environ.get("PTL_MOE_TC", "1") != "0"
     MOE_WIDE_MIN_ROWS = int(os.environ.get("PTL_MOE_WIDE_MIN", "512"))   # (token, choice) pairs from which tiles of 128 rows pay
