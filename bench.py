@@ -3,6 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --family tibepel      # another workload: the Tibepel decoder beside a Llama of equal size
     python bench.py --family lilenex      # likewise the Lilenex decoder
+    python bench.py --family sogalix      # the Sogalix decoder beside a Lilenex and a Llama of equal size
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and context 4096, timed on
 the device with CUDA events around exactly K decode steps (a step = the engine's step function for
@@ -193,10 +194,37 @@ def _lilenex(width, layers, ff, vocab):
             "layers": out}
 
 
+def _sogalix(width, layers, ff, vocab):
+    """A Sogalix of sizes that resemble a real model's layers.  Of every four layers the first is attention through latents
+    (heads of 128 plain + 64 rotated entries, values of 128, a key/value latent of 512 and a query latent of 3/4 width), the
+    second a generalized delta rule (heads of 64 x 64), the third softmax attention with the sink term and a query
+    temperature (heads of 128, 4 query heads per kv head), the fourth attention through latents over what the first keeps.
+    Every layer has the dense xIELU feed-forward."""
+    heads = width // 128
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 3 * width // 4, "scale": 192 ** -0.5,
+           "rot": {"dims": 64, "base": 1000000.0}}
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "q_temp": {"coef": 0.1, "every": 512}}
+    delta = {"heads": width // 64, "dim": 64, "rank": 64}
+    mlp = {"kind": "dense", "ff": ff}
+    out = []
+    for i in range(layers):
+        if i % 4 == 1:
+            out.append({"type": "general_delta", "mixer": delta, "mlp": mlp})
+        elif i % 4 == 2:
+            out.append({"type": "attention", "mixer": att, "mlp": mlp})
+        else:
+            out.append({"type": "latent_attention", "mixer": dict(lat, kv_from=i - 3) if i % 4 == 3 else lat, "mlp": mlp})
+    return {"architecture": "Sogalix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": out}
+
+
+FAMILIES = {"tibepel": (_tibepel, ["llama"]), "lilenex": (_lilenex, ["llama"]), "sogalix": (_sogalix, ["lilenex", "llama"])}
+
+
 def family_bench(args) -> int:
-    """``--family tibepel`` or ``--family lilenex``: prefill (one step of 2,048 prompt tokens, as one prompt and as 8 prompts of 256) and decode
-    (8 requests at 1,024 tokens, a step with its sampling kernel) of that decoder and of a Llama decoder of the same width, depth, feed-forward size
-    and vocabulary, on random weights, timed with CUDA events after warm-up; then one timed step of each kind with
+    """``--family tibepel``, ``lilenex`` or ``sogalix``: prefill (one step of 2,048 prompt tokens, as one prompt and as 8 prompts of 256) and decode
+    (8 requests at 1,024 tokens, a step with its sampling kernel) of that decoder and of a Llama decoder (for Sogalix also a Lilenex decoder) of the
+    same width, depth, feed-forward size and vocabulary, on random weights, timed with CUDA events after warm-up; then one timed step of each kind with
     every operator bracketed by events, for the milliseconds by class of kernels.  One JSON line."""
     import torch
     from pytriton_llama_b200.config import EngineConfig
@@ -211,8 +239,11 @@ def family_bench(args) -> int:
     toks = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
     rows = []
     for width, layers, ff in sizes:
-        models = {args.family: (_tibepel if args.family == "tibepel" else _lilenex)(width, layers, ff, vocab),
-                  "llama": dict(_llama(layers, width, width // 128, max(1, width // 512), 128, ff, 32.0, False), vocab_size=vocab)}
+        make, beside = FAMILIES[args.family]
+        models = {args.family: make(width, layers, ff, vocab)}
+        for other in beside:
+            models[other] = FAMILIES[other][0](width, layers, ff, vocab) if other != "llama" else \
+                dict(_llama(layers, width, width // 128, max(1, width // 512), 128, ff, 32.0, False), vocab_size=vocab)
         row = {"width": width, "layers": layers, "ff": ff, "vocab": vocab}
         for name, cfg in models.items():
             pages = (batch + 1) * (-(-(context + K + W + 8) // 16)) + 2 * (-(-prompt_len // 16))
@@ -283,7 +314,8 @@ def family_bench(args) -> int:
             del engine
             torch.cuda.empty_cache()
         rows.append(row)
-    print(json.dumps({"metric": "family_tokens_per_s", "family": args.family, "beside": "llama of equal width, depth, feed-forward and vocabulary",
+    print(json.dumps({"metric": "family_tokens_per_s", "family": args.family,
+                      "beside": " and ".join(FAMILIES[args.family][1]) + " of equal width, depth, feed-forward and vocabulary",
                       "dtype": args.dtype, "data": "synthetic", "n_gpus": 1, "steps": K, "warmup": W,
                       "workload": {"prefill_tokens": prompt_len, "decode_batch": batch, "decode_context": context},
                       "peaks": dict(peaks, kind=peak_kind), "sizes": rows}))
@@ -327,7 +359,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=None, help="decode batch (default: 8; 32 for 3b; 64 for 8b)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--points", default=None, help="extra decode batch sizes, comma separated ('' for none)")
-    ap.add_argument("--family", default=None, choices=["tibepel", "lilenex"],
+    ap.add_argument("--family", default=None, choices=["tibepel", "lilenex", "sogalix"],
                     help="another workload: this decoder beside a Llama of equal size, prefill and decode (own JSON line)")
     ap.add_argument("--family-sizes", default=None, help="with --family: WIDTHxLAYERSxFF[,...] (default 1024x8x4096,2048x8x8192)")
     ap.add_argument("--no-e2e", action="store_true")

@@ -195,7 +195,7 @@ int qk_norm_rotate_store(void* proj, int tokens, int ld, int H, int G, int d, in
 }
 
 // ------------------------------------------------------------------ attention
-constexpr int kWaMaxPerLane = 8;   // value heads up to 256
+constexpr int kWaMaxPerLane = 16;  // value heads up to 512 (kernels are built for 8 and for 16 values per lane)
 constexpr int kWaWarps = 4;
 
 __device__ __forceinline__ void wa_two_fma(float& hi, float& lo, float a, float b) {
@@ -216,7 +216,7 @@ __device__ __forceinline__ void wa_two_scale(float& hi, float& lo, float c) {
   hi = h;
 }
 
-template <typename T>
+template <typename T, int MPL>
 __global__ void __launch_bounds__(kWaWarps * 32)
 window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_table,
@@ -224,6 +224,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
                         int bt_stride, int H, int G, int d, int dv, int page_size, float scale, int window, int keep,
                         int splits, int num_pages, int vec_ok, const int* __restrict__ items, int wide_ok, int shared_v,
                         int sink, float temp_coef, int temp_every) {
+  constexpr int kWaMaxPerLane = MPL;   // values of a head that a lane holds
   extern __shared__ float qs_all[];  // [warps][d]
   __shared__ float s_pr[kWaWarps][32];
   __shared__ unsigned long long s_vb[kWaWarps][32];
@@ -413,10 +414,11 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
 }
 
 // out = sum_z e^{m_z - M} acc_z / sum_z e^{m_z - M} l_z over the parts of the key list, in the order of the parts.
-template <typename T>
+template <typename T, int MPL>
 __global__ void __launch_bounds__(kWaWarps * 32)
 window_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                               int out_stride, int H, int dv, int splits, int tokens, const int* __restrict__ items, int sink) {
+  constexpr int kWaMaxPerLane = MPL;
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -507,18 +509,21 @@ int window_attention(void* out, const void* q, const void* cache, const int* blo
     wide_ok = dv / 32;
   dim3 grid(tokens, (H + kWaWarps - 1) / kWaWarps, splits);
   const size_t smem = (size_t)kWaWarps * d * sizeof(float);
-  int rc = launch_kernel("window_attention", window_attention_kernel<T>, grid, dim3(kWaWarps * 32), smem, as_stream(stream),
-                         (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req, positions, q_stride,
-                         out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages, vec_ok, items, wide_ok,
-                         shared_v, sink, temp_coef, temp_every);
-  if (rc) return rc;
-  if (splits > 1) {
-    const long long pairs = (long long)tokens * H;
-    rc = launch_kernel("window_attention_merge", window_attention_merge_kernel<T>,
-                       dim3((unsigned)((pairs + kWaWarps - 1) / kWaWarps)), dim3(kWaWarps * 32), 0, as_stream(stream), (T*)out,
-                       (const float*)part_acc, (const float*)part_ml, out_stride, H, dv, splits, tokens, items, sink);
+  const long long pairs = (long long)tokens * H;
+#define PTL_WA_LAUNCH(MPL)                                                                                                         \
+  {                                                                                                                                \
+    int rc = launch_kernel("window_attention", window_attention_kernel<T, MPL>, grid, dim3(kWaWarps * 32), smem,                   \
+                           as_stream(stream), (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req,      \
+                           positions, q_stride, out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits,        \
+                           num_pages, vec_ok, items, wide_ok, shared_v, sink, temp_coef, temp_every);                              \
+    if (rc || splits <= 1) return rc;                                                                                              \
+    return launch_kernel("window_attention_merge", window_attention_merge_kernel<T, MPL>,                                          \
+                         dim3((unsigned)((pairs + kWaWarps - 1) / kWaWarps)), dim3(kWaWarps * 32), 0, as_stream(stream), (T*)out,  \
+                         (const float*)part_acc, (const float*)part_ml, out_stride, H, dv, splits, tokens, items, sink);           \
   }
-  return rc;
+  if (dv <= 32 * 8) PTL_WA_LAUNCH(8)      // (value heads up to 256 keep the registers of 8 values per lane)
+  PTL_WA_LAUNCH(16)
+#undef PTL_WA_LAUNCH
 }
 
 }  // namespace ptl

@@ -459,7 +459,7 @@ class TorchOps:
         if R:
             c = unit(x[:, Q:Q + R]) * kv_norm.double()
             kr = x[:, Q + R:Q + R + n].clone()
-            ang = positions.double()[:, None] * freq.double()[None, :dims // 2]
+            ang = (positions.float()[:, None] * freq.float()[None, :dims // 2]).double()   # the angle is a float32 product
             a, b = kr[:, 0:dims:2].clone(), kr[:, 1:dims:2].clone()
             kr[:, 0:dims:2] = a * ang.cos() - b * ang.sin()
             kr[:, 1:dims:2] = b * ang.cos() + a * ang.sin()
@@ -483,7 +483,7 @@ class TorchOps:
     def rotate_head_part(self, x, x_ld, x_col, out, out_ld, out_col, H, n, positions, freq, dims):
         T = x.shape[0]
         part = x.double().view(T, H, x_ld)[:, :, x_col:x_col + n].clone()
-        ang = positions.double()[:, None] * freq.double()[None, :dims // 2]
+        ang = (positions.float()[:, None] * freq.float()[None, :dims // 2]).double()   # the angle is a float32 product
         c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
         a, b = part[..., 0:dims:2].clone(), part[..., 1:dims:2].clone()
         part[..., 0:dims:2] = a * c - b * s
