@@ -42,7 +42,8 @@ __global__ void __launch_bounds__(PrefillCfg<D, MT>::kThreads)
 prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q,
                          const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table,
                          const int* __restrict__ tiles, int q_stride, int out_stride, int bt_stride, int nq,
-                         int nkv, int page_size, float scale_log2, int window, int num_pages, int page_shift, int keep) {
+                         int nkv, int page_size, float scale_log2, int window, int num_pages, int page_shift, int keep,
+                         int sink, float temp_coef, int temp_every) {
   using Cfg = PrefillCfg<D, MT>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_pages[kPfStagedPages];
@@ -138,9 +139,15 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
 
   const int warp_qmin = pos0 + wrow0, warp_qmax = pos0 + wrow0 + 16 * MT - 1;
   float m_run[MT][2], l_run[MT][2];
+  float row_scale[MT][2];                          // the scores' factor of a row: the scale, times the query temperature of its position
   float o[MT][D / 8][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int qp = pos0 + wrow0 + mt * 16 + g + hh * 8;
+      row_scale[mt][hh] = temp_coef != 0.f ? scale_log2 * fmaf(temp_coef, logf((float)((qp + 1) / temp_every) + 1.0f), 1.0f) : scale_log2;
+    }
     m_run[mt][0] = m_run[mt][1] = -INFINITY;
     l_run[mt][0] = l_run[mt][1] = 0.f;
 #pragma unroll
@@ -193,7 +200,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
       for (int nt = 0; nt < kPfKeys / 8; ++nt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float v = s[mt][nt][e] * scale_log2;
+          float v = s[mt][nt][e] * row_scale[mt][e >> 1];
           if (need_mask) {
             const int key = key_first + nt * 8 + 2 * c + (e & 1);
             const int qp = qpos0 + (e >> 1) * 8;
@@ -251,6 +258,13 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
     for (int hh = 0; hh < 2; ++hh) {
       const int row = wrow0 + mt * 16 + g + hh * 8;
       if (row >= rows) continue;
+      if (sink) {       // one more term of score 0 and no value: the maximum may move to 0, and 2^(0 - maximum) joins the sum
+        const float m_all = fmaxf(m_run[mt][hh], 0.f);
+        const float a = exp2f(m_run[mt][hh] - m_all);
+        l_run[mt][hh] = fmaf(l_run[mt][hh], a, exp2f(-m_all));
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[mt][i][2 * hh] *= a; o[mt][i][2 * hh + 1] *= a; }
+      }
       const float inv = l_run[mt][hh] > 0.f ? 1.0f / l_run[mt][hh] : 0.f;
       __nv_bfloat16* dst = out + (size_t)(tok0 + row) * out_stride + (size_t)h * D + 2 * c;
 #pragma unroll
@@ -263,7 +277,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
 template <int D, int MT>
 int launch_prefill(void* out, const void* q, const void* cache, const int* block_table, const int* tiles, int n_tiles,
                    int q_stride, int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale,
-                   int window, int num_pages, void* stream, int keep = 0) {
+                   int window, int num_pages, void* stream, int keep = 0, int sink = 0, float temp_coef = 0.f, int temp_every = 1) {
   using Cfg = PrefillCfg<D, MT>;
   static SmemRaised raised = {};
   if (int rc = raise_shared_memory("prefill_attention", prefill_attention_kernel<D, MT>, Cfg::kSmem, raised)) return rc;
@@ -274,7 +288,7 @@ int launch_prefill(void* out, const void* q, const void* cache, const int* block
   return launch_kernel("prefill_attention", prefill_attention_kernel<D, MT>, grid, dim3(Cfg::kThreads), Cfg::kSmem,
                        as_stream(stream), (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache,
                        block_table, tiles, q_stride, out_stride, bt_stride, nq, nkv, page_size,
-                       scale * 1.4426950408889634f, window, num_pages, page_shift, keep);
+                       scale * 1.4426950408889634f, window, num_pages, page_shift, keep, sink, temp_coef, temp_every);
 }
 
 }  // namespace ptl
@@ -316,4 +330,27 @@ PTL_EXPORT int ptl_prefill_attention_keep_bf16(void* out, const void* q, const v
                                          page_size, scale, window, num_pages, stream, keep);
   return launch_prefill<128, 1>(out, q, cache, block_table, tiles, n_tiles, q_stride, out_stride, bt_stride, nq, nkv,
                                 page_size, scale, window, num_pages, stream, keep);
+}
+
+// The same with the options of the window attention's other kernel: `sink` adds one term of score 0 (and no value) to
+// every softmax's denominator; `temp_coef` != 0 multiplies the scores of the query at position p by
+// 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1).
+PTL_EXPORT int ptl_prefill_attention_opts_bf16(void* out, const void* q, const void* cache, const int* block_table,
+                                               const int* tiles, int n_tiles, int q_stride, int out_stride, int bt_stride,
+                                               int nq, int nkv, int d, int page_size, float scale, int window, int keep,
+                                               int num_pages, int sink, float temp_coef, int temp_every, void* stream) {
+  using namespace ptl;
+  PTL_REQUIRE(n_tiles >= 0 && nq > 0 && nkv > 0 && page_size > 0 && num_pages > 0 && keep >= 0 && temp_every >= 1,
+              "prefill_attention: bad sizes");
+  PTL_REQUIRE(nq % nkv == 0, "prefill_attention: %d query heads are no multiple of %d kv heads", nq, nkv);
+  if (d != 64 && d != 128) return -2;
+  PTL_REQUIRE(aligned16(q) && aligned16(cache) && aligned16(out) && q_stride % 8 == 0 && out_stride % 2 == 0,
+              "prefill_attention: q, cache and out must be 16-byte aligned");
+  if (n_tiles == 0) return 0;
+  if (window == 0) keep = 0;
+  if (d == 64)
+    return launch_prefill<64, PTL_PF_MT>(out, q, cache, block_table, tiles, n_tiles, q_stride, out_stride, bt_stride, nq, nkv,
+                                         page_size, scale, window, num_pages, stream, keep, sink, temp_coef, temp_every);
+  return launch_prefill<128, 1>(out, q, cache, block_table, tiles, n_tiles, q_stride, out_stride, bt_stride, nq, nkv,
+                                page_size, scale, window, num_pages, stream, keep, sink, temp_coef, temp_every);
 }

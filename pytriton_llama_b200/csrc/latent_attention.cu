@@ -9,9 +9,70 @@
 //
 // rotate_head_part, per token and head: n entries at column x_col of a head of x (rows of heads * x_ld) are copied to
 // column out_col of the same head of out (rows of heads * out_ld), the pairs (2i, 2i+1), i < dims/2, turned likewise.
+//
+// For prompt portions the attention over the latents is made of matrix products (ops/cuda.py, latent_prefill_attention):
+// latent_gather copies one request's kept rows [c | k_r] out of its pages into consecutive rows, and the latents c once
+// more with keys along the rows (the second product's right operand); causal_softmax_rows turns a float32 block of
+// scores, one row per (token, head), into the weights of the keys up to the token's own position (float32 maximum, sum
+// and quotient; rounded once) and zeros beyond.
 #include "common.cuh"
 
 namespace ptl {
+
+// keys [c_pad, d] and latents_t [R, c_pad] of the request whose block table row is bt: key j < ctx comes from its page,
+// rows and columns from ctx to c_pad are zero.  One block per 32 keys; the tile passes shared memory so that both
+// copies are written along their rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_gather_kernel(T* __restrict__ keys, T* __restrict__ latents_t, const T* __restrict__ cache, const int* __restrict__ bt,
+                     int ctx, int c_pad, int d, int R, int page_size, int num_pages) {
+  extern __shared__ __align__(16) unsigned char lg_raw[];
+  T* tile = reinterpret_cast<T*>(lg_raw);          // [32][d + 2]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int ld = d + 2;
+  const int k0 = blockIdx.x * 32;
+  for (int idx = threadIdx.x; idx < 32 * d; idx += blockDim.x) {
+    const int row = idx / d, e = idx % d;
+    const int key = k0 + row;
+    T v = from_f32<T>(0.f);
+    if (key < ctx) {
+      const int page = bt[key / page_size];
+      if (page >= 0 && page < num_pages) v = cache[((size_t)page * page_size + key % page_size) * d + e];
+    }
+    tile[row * ld + e] = v;
+    if (key < c_pad) keys[(size_t)key * d + e] = v;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (k0 + lane < c_pad)
+    for (int e = warp; e < R; e += 8) latents_t[(size_t)e * c_pad + k0 + lane] = tile[lane * ld + e];
+}
+
+// weights[row, j] = exp(scale * s[row, j] - m) / sum for j <= position of the row's token (j < n_keys), 0 for the other
+// j < ld_out; with `sink` the sum has one more term exp(0 - m).  Row = token * heads + head.  One block per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+causal_softmax_rows_kernel(T* __restrict__ weights, int ld_out, const float* __restrict__ scores, int n_keys,
+                           const int* __restrict__ positions, int heads, float scale, int sink) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t row = blockIdx.x;
+  const int p = positions[row / heads];
+  const int n = min(p + 1, n_keys);
+  const float* s = scores + row * (size_t)n_keys;
+  T* w = weights + row * (size_t)ld_out;
+  float m = sink ? 0.f : -INFINITY;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) m = fmaxf(m, s[j] * scale);
+  m = block_max(m, red);
+  float sum = 0.f;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) sum += expf(s[j] * scale - m);
+  sum = block_sum(sum, red);
+  if (sink) sum += expf(-m);
+  const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+  for (int j = threadIdx.x; j < ld_out; j += blockDim.x) w[j] = from_f32<T>(j < n ? expf(s[j] * scale - m) * inv : 0.f);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -105,6 +166,26 @@ int rotate_head_part(void* out, int out_ld, int out_col, const void* x, int x_ld
                        out_col, (const T*)x, x_ld, x_col, heads, n, positions, freq, dims);
 }
 
+template <typename T>
+int latent_gather(void* keys, void* latents_t, const void* cache, const int* bt, int ctx, int c_pad, int d, int R, int page_size,
+                  int num_pages, void* stream) {
+  PTL_REQUIRE(ctx >= 0 && c_pad >= ctx && d > 0 && R > 0 && R <= d && page_size > 0 && num_pages > 0, "latent_gather: bad sizes");
+  const size_t smem = (size_t)32 * (d + 2) * sizeof(T);
+  PTL_REQUIRE(smem <= 48 * 1024, "latent_gather: rows of %d entries do not fit shared memory", d);
+  if (c_pad == 0) return 0;
+  return launch_kernel("latent_gather", latent_gather_kernel<T>, dim3((c_pad + 31) / 32), dim3(256), smem, as_stream(stream),
+                       (T*)keys, (T*)latents_t, (const T*)cache, bt, ctx, c_pad, d, R, page_size, num_pages);
+}
+
+template <typename T>
+int causal_softmax_rows(void* weights, int ld_out, const float* scores, long long rows, int n_keys, const int* positions,
+                        int heads, float scale, int sink, void* stream) {
+  PTL_REQUIRE(rows >= 0 && rows < (1ll << 31) && n_keys > 0 && ld_out >= n_keys && heads > 0, "causal_softmax_rows: bad sizes");
+  if (rows == 0) return 0;
+  return launch_kernel("causal_softmax_rows", causal_softmax_rows_kernel<T>, dim3((unsigned)rows), dim3(256), 0, as_stream(stream),
+                       (T*)weights, ld_out, scores, n_keys, positions, heads, scale, sink);
+}
+
 }  // namespace ptl
 
 #define PTL_LATENT(SUFFIX, TYPE)                                                                                                  \
@@ -118,5 +199,16 @@ int rotate_head_part(void* out, int out_ld, int out_col, const void* x, int x_ld
                                               int heads, int n, const int* positions, const float* freq, int dims, void* stream) { \
     return ptl::rotate_head_part<TYPE>(out, out_ld, out_col, x, x_ld, x_col, tokens, heads, n, positions, freq, dims, stream);     \
   }
+#define PTL_LATENT_PREFILL(SUFFIX, TYPE)                                                                                          \
+  PTL_EXPORT int ptl_latent_gather##SUFFIX(void* keys, void* latents_t, const void* cache, const int* bt, int ctx, int c_pad,      \
+                                           int d, int R, int page_size, int num_pages, void* stream) {                           \
+    return ptl::latent_gather<TYPE>(keys, latents_t, cache, bt, ctx, c_pad, d, R, page_size, num_pages, stream);                  \
+  }                                                                                                                               \
+  PTL_EXPORT int ptl_causal_softmax_rows##SUFFIX(void* weights, int ld_out, const float* scores, long long rows, int n_keys,       \
+                                                 const int* positions, int heads, float scale, int sink, void* stream) {          \
+    return ptl::causal_softmax_rows<TYPE>(weights, ld_out, scores, rows, n_keys, positions, heads, scale, sink, stream);          \
+  }
+PTL_LATENT_PREFILL(_f32, float)
+PTL_LATENT_PREFILL(_bf16, __nv_bfloat16)
 PTL_LATENT(_f32, float)
 PTL_LATENT(_bf16, __nv_bfloat16)

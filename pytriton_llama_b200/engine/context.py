@@ -55,6 +55,7 @@ class StepContext:
     groups: Dict[int, GroupStepView] = field(default_factory=dict)
     q_lens: List[int] = field(default_factory=list)       # host copies for launch decisions
     ctx_lens: List[int] = field(default_factory=list)
+    host_lengths_exact: bool = False    # q_lens and ctx_lens are this step's own (not those a captured step was laid out for)
     max_q_len: int = 0
     max_ctx_len: int = 0
     attn_splits: int = 1

@@ -188,6 +188,7 @@ class Engine:
         self.stats = EngineStats()
         if self.config.timing and hasattr(self.ops, "enable_timing"):
             self.ops.enable_timing()
+        self._portions_by_host_lengths = self.model.any_part(lambda part: getattr(part, "portions_by_host_lengths", False))
         self._graphs = {}          # captured steps: padded batch size or _DecodeShape (single tokens only), or a shape tuple
         self._shape_seen: Dict[tuple, int] = {}
         self._shape_captures = 0
@@ -304,6 +305,7 @@ class Engine:
                                             self._choose_splits(batch.T, max(s + n for s, n in zip(starts, q_lens))),
                                             work_items=self._work_items(batch.work),
                                             in_order=self._work_in_order(batch.work, batch.T))
+            ctx.host_lengths_exact = True
             logits = self.model.forward(layout.view(dev, "tokens"), ctx, cache_view,
                                         layout.view(dev, "logit_rows") if logit_rows else None)
         out = StepOutput(logits, rows, batch.T, batch.R)
@@ -434,6 +436,8 @@ class Engine:
         if any(grp.state for grp in self.cache.groups) or not any(grp.paged for grp in self.cache.groups):
             return 0
         if batch.max_q_len != 1:
+            if self._portions_by_host_lengths:
+                return 0      # a mixer lays its prompt portions out by the step's own lengths, which a captured shape does not have
             return self._shape_bucket(batch) if self.config.capture_mixed_steps else 0
         b = 1
         while b < batch.R:

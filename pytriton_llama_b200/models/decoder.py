@@ -38,6 +38,10 @@ class DecoderModel:
             roots.append((self.embedding_norm, self.spec.embedding_norm))
         return roots
 
+    def any_part(self, predicate) -> bool:
+        """True if ``predicate`` holds for a part of the model (nested parts included)."""
+        return any(predicate(part) for root, rspec in self._roots() for part, _ in _walk(root, rspec))
+
     # ------------------------------------------------------------------ tensors
     def expected_tensors(self) -> Dict[str, TensorSpec]:
         """Checkpoint name -> spec of every tensor the model reads."""

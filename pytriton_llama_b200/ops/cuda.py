@@ -56,6 +56,8 @@ _SIGNATURES = {
     "ptl_latent_norm_store": [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr, _c_int, _c_f, _ptr, _ptr, _c_int, _ptr, _ptr,
                               _c_ll, _ptr],
     "ptl_rotate_head_part": [_ptr, _c_int, _c_int, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr],
+    "ptl_latent_gather": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr],
+    "ptl_causal_softmax_rows": [_ptr, _c_int, _ptr, _c_ll, _c_int, _ptr, _c_int, _c_f, _c_int, _ptr],
     "ptl_head_linear": [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr],
     "ptl_gla_scan": [_ptr, _ptr, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr],
     "ptl_moe_gather": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr],
@@ -156,9 +158,9 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_sample_work_words.restype = _c_int
     lib.ptl_softcap.argtypes = [_ptr, _c_ll, _c_f, _ptr]
     lib.ptl_softcap.restype = _c_int
-    lib.ptl_prefill_attention_keep_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                                    _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _ptr]
-    lib.ptl_prefill_attention_keep_bf16.restype = _c_int
+    lib.ptl_prefill_attention_opts_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                    _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _ptr]
+    lib.ptl_prefill_attention_opts_bf16.restype = _c_int
     lib.ptl_moe_tile_rows.argtypes = []
     lib.ptl_moe_tile_rows.restype = _c_int
     lib.ptl_moe_route.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
@@ -253,7 +255,8 @@ class CudaOps:
             info = self.WORK_LISTS[name]
             t = torch.tensor(values if values else [0], dtype=torch.int32, device=self.device)[:len(values)]
             work[name] = StepWork(t, len(values) // info.width, info.width == 1 and values == list(range(T)))
-        return SimpleNamespace(work=work, max_ctx_len=max(ctx_lens))
+        return SimpleNamespace(work=work, max_ctx_len=max(ctx_lens), q_lens=list(q_lens), ctx_lens=list(ctx_lens),
+                               host_lengths_exact=True)
 
     @staticmethod
     def _work(hints, name):
@@ -274,6 +277,7 @@ class CudaOps:
         "gla_scan": "recurrent", "routed_experts": "experts",
         "add_layernorm": "norm", "xielu": "elementwise", "lowrank_tanh_linear": "recurrent", "general_delta_scan": "recurrent",
         "latent_norm_store": "rope", "rotate_head_part": "rope", "head_linear": "product",
+        "latent_gather": "attention", "causal_softmax_rows": "attention",
     }
 
     def enable_timing(self) -> None:
@@ -1102,24 +1106,17 @@ class CudaOps:
         tokens = q.shape[0]
         out = self.empty((tokens, H * dv), q.dtype)
         options = (int(bool(shared_values)), int(bool(sink)), float(temp_coef), int(temp_every))
-        if options != (0, 0, 0.0, int(temp_every)):
-            longest = getattr(hints, "max_ctx_len", 0) or block_table.shape[1] * page_size
-            if window:
-                longest = min(longest, window + keep_first)
-            self._window_attention_simt(out, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window,
-                                        keep_first, self._window_splits(tokens, H, longest), None, options)
-            return out
-        if (q.dtype == torch.bfloat16 and d == dv and d in (64, 128) and self._work(hints, "prefill_tiles") is not None
+        if (q.dtype == torch.bfloat16 and d == dv and d in (64, 128) and not shared_values and self._work(hints, "prefill_tiles") is not None
                 and self._work(hints, "decode_items") is not None and os.environ.get("PTL_WINDOW_TC", "1") != "0"):
             if self._window_attention_tensor_cores(out, q, cache, block_table, tok_req, positions, H, G, d, page_size, scale,
-                                                   window, keep_first, hints):
+                                                   window, keep_first, hints, options):
                 return out
         longest = getattr(hints, "max_ctx_len", 0) or block_table.shape[1] * page_size
         if window:
             longest = min(longest, window + keep_first)
         splits = self._window_splits(tokens, H, longest)
         self._window_attention_simt(out, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window,
-                                    keep_first, splits, None)
+                                    keep_first, splits, None, options)
         return out
 
     def _window_splits(self, tokens: int, H: int, longest: int) -> int:
@@ -1144,15 +1141,16 @@ class CudaOps:
                     kernels=2 if splits > 1 else 1)
 
     def _window_attention_tensor_cores(self, out, q, cache, block_table, tok_req, positions, H, G, d, page_size, scale, window,
-                                       keep_first, hints) -> bool:
+                                       keep_first, hints, options=(0, 0, 0.0, 1)) -> bool:
         """bfloat16, key and value heads of 64 or 128: the portions of a step on the tensor cores (the warp-level prompt
         kernel, which walks the kept first keys as key tiles of their own before the window's), its single tokens on
         the CUDA-core kernel with their key lists split; both write their rows of ``out``."""
         dec, tiles = hints.work["decode_items"], hints.work["prefill_tiles"]
         if tiles.items:
-            rc = self.lib.ptl_prefill_attention_keep_bf16(
+            rc = self.lib.ptl_prefill_attention_opts_bf16(
                 _p(out), _p(q), _p(cache), _p(block_table), _p(tiles.tensor), tiles.items, q.shape[1], H * d, block_table.shape[1],
-                H, G, d, page_size, float(scale), int(window), int(keep_first), cache.shape[0], self._stream())
+                H, G, d, page_size, float(scale), int(window), int(keep_first), cache.shape[0], options[1], options[2], options[3],
+                self._stream())
             if rc == -2:
                 return False
             self._check(rc)
@@ -1162,7 +1160,7 @@ class CudaOps:
                 longest = min(longest, window + keep_first)
             self._window_attention_simt(out, q, cache, block_table, tok_req, positions, H, G, d, d, page_size, scale, window,
                                         keep_first, self._window_splits(dec.items, H, longest),
-                                        (None if dec.in_order else dec.tensor, dec.items))
+                                        (None if dec.in_order else dec.tensor, dec.items), options)
         return True
 
     def gla_scan(self, proj: torch.Tensor, z: torch.Tensor, bias: torch.Tensor, inv_tau: float, state: torch.Tensor, ctx, H: int,
@@ -1280,6 +1278,85 @@ class CudaOps:
                        float(eps), _p(positions), _p(freq) if R else None, int(dims) if R else 0, _p(slots) if R else None,
                        _p(cache) if R else None, num_slots, self._stream()))
         return out
+
+    LATENT_QUERY_CHUNK = 512        # tokens whose scores against a request's keys are held at a time (all heads)
+
+    def latent_attention(self, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, ctx, H: int, R: int, n: int,
+                         page_size: int, scale: float) -> torch.Tensor:
+        """Causal softmax attention of H query heads over one kept row [latent (R) | rotated key part (n)] per
+        position, the latent being the value: q [T, H*(R+n)] -> [T, H*R].  Single tokens, float32 and steps whose
+        host lengths are not the step's own (a captured shape) take the paged kernel; in bfloat16 every prompt
+        portion of a step whose context says its host lengths are exact is worked as two tensor-core products
+        around a float32 softmax, per request and per ``LATENT_QUERY_CHUNK`` tokens: all heads' queries of the
+        chunk against the request's gathered rows, the weights (rounded once) against the gathered latents."""
+        d = R + n
+        portions = [(r, qn) for r, qn in enumerate(getattr(ctx, "q_lens", []) or []) if qn > 1]
+        dec = self._work(ctx, "decode_items")
+        composed = (q.dtype == torch.bfloat16 and portions and getattr(ctx, "host_lengths_exact", False) and dec is not None
+                    and 32 * (d + 2) * 2 <= 48 * 1024 and os.environ.get("PTL_LATENT_PRODUCTS", "1") != "0")
+        if not composed:
+            return self.window_attention(q, cache, block_table, ctx.tok_req, ctx.positions, H, 1, d, R, page_size, scale,
+                                         splits=getattr(ctx, "attn_splits", 1), hints=ctx, shared_values=True)
+        self._want(q, "q")
+        self._want(cache, "cache", q.dtype)
+        if cache[0].numel() != page_size * d or q.shape[1] != H * d:
+            raise KernelError("latent_attention: the cache's pages or the queries do not fit the sizes")
+        T = q.shape[0]
+        out = self.empty((T, H * R), q.dtype)
+        if dec.items:       # the step's single tokens: the paged kernel on their rows
+            longest = getattr(ctx, "max_ctx_len", 0) or block_table.shape[1] * page_size
+            self._window_attention_simt(out, q, cache, block_table, ctx.tok_req, ctx.positions, H, 1, d, R, page_size, scale, 0, 0,
+                                        self._window_splits(dec.items, H, longest),
+                                        (None if dec.in_order else dec.tensor, dec.items), (1, 0, 0.0, 1))
+        t0 = 0
+        starts = {}
+        for r, qn in enumerate(ctx.q_lens):
+            starts[r] = t0
+            t0 += qn
+        for r, qn in portions:
+            c = int(ctx.ctx_lens[r])
+            c_pad = -(-c // 64) * 64
+            keys = self.empty((c_pad, d), q.dtype)
+            latents_t = self.empty((R, c_pad), q.dtype)
+            self.latent_gather(keys, latents_t, cache, block_table, r, c, R, page_size)
+            first = c - qn                                  # position of the portion's first token
+            for a in range(0, qn, self.LATENT_QUERY_CHUNK):
+                b = min(qn, a + self.LATENT_QUERY_CHUNK)
+                rows = slice(starts[r] + a, starts[r] + b)
+                n_keys = min(c_pad, -(-(first + b) // 64) * 64)      # no row of the chunk sees a later key
+                scores = self.linear(q[rows].view((b - a) * H, d), keys[:n_keys], out_dtype=torch.float32)
+                weights = self.empty(((b - a) * H, c_pad), q.dtype)
+                self.causal_softmax_rows(weights, scores, ctx.positions, rows.start, H, scale)
+                out[rows] = self.linear(weights, latents_t).view(b - a, H * R)
+        return out
+
+    def latent_gather(self, keys: torch.Tensor, latents_t: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, r: int,
+                      ctx_len: int, R: int, page_size: int) -> None:
+        """keys [c_pad, d] <- the first ctx_len kept rows of the request in row r of the block table (zeros after them);
+        latents_t [R, c_pad] <- their first R entries, keys along the rows."""
+        self._want(keys, "keys", cache.dtype)
+        self._want(latents_t, "latents_t", cache.dtype)
+        self._want(block_table, "block_table", torch.int32)
+        c_pad, d = keys.shape
+        if tuple(latents_t.shape) != (R, c_pad) or cache[0].numel() != page_size * d or not 0 <= r < block_table.shape[0]:
+            raise KernelError("latent_gather: shapes do not fit")
+        fn = getattr(self.lib, "ptl_latent_gather" + _suffix(cache.dtype))
+        self._check(fn(_p(keys), _p(latents_t), _p(cache), block_table.data_ptr() + 4 * r * block_table.shape[1], int(ctx_len), c_pad,
+                       d, R, page_size, cache.shape[0], self._stream()))
+
+    def causal_softmax_rows(self, weights: torch.Tensor, scores: torch.Tensor, positions: torch.Tensor, first_token: int, H: int,
+                            scale: float, sink: bool = False) -> None:
+        """scores float32 [tokens*H, n_keys] (row = token * H + head, tokens from ``first_token`` of the step on) ->
+        weights [tokens*H, >= n_keys]: softmax of scale * score over the keys up to the token's position, zeros beyond."""
+        self._want(scores, "scores", torch.float32)
+        self._want(weights, "weights")
+        self._want(positions, "positions", torch.int32)
+        rows, n_keys = scores.shape
+        if weights.shape[0] != rows or weights.shape[1] < n_keys or rows % H or first_token + rows // H > positions.shape[0]:
+            raise KernelError("causal_softmax_rows: shapes do not fit")
+        fn = getattr(self.lib, "ptl_causal_softmax_rows" + _suffix(weights.dtype))
+        self._check(fn(_p(weights), weights.shape[1], _p(scores), rows, n_keys, positions.data_ptr() + 4 * first_token, H,
+                       float(scale), int(bool(sink)), self._stream()))
 
     def head_linear(self, x: torch.Tensor, x_ld: int, x_col: int, w: torch.Tensor, out: torch.Tensor, out_ld: int, out_col: int,
                     H: int, gate: Optional[torch.Tensor] = None, gate_column: int = 0) -> None:

@@ -43,6 +43,8 @@ class LatentAttention(Part):
         self.scale, self.eps = float(p["scale"]), float(p["norm_eps"])
         self.own_kv = bool(p.get("own_kv", True))
         self.position = build_part("position", spec.parts["position"], runtime)
+        # in bfloat16 the operator works prompt portions as matrix products laid out by the step's own lengths
+        self.portions_by_host_lengths = runtime.dtype == torch.bfloat16
 
     def children(self):
         return {"position": self.position}
@@ -86,8 +88,7 @@ class LatentAttention(Part):
         ql = ops.empty((T, H * (R + n)), self.rt.dtype)                        # [T, H, q_c | rotated]
         ops.head_linear(q, d + n, 0, self.w_uk_t, ql, R + n, 0, H)             # q_c = W_uk[n]^T q_plain
         ops.rotate_head_part(q, d + n, d, ql, R + n, R, H, n, ctx.positions, freq, dims)
-        o = ops.window_attention(ql, cache.kv, g.block_table, ctx.tok_req, ctx.positions, H, 1, R + n, R, g.page_size, self.scale,
-                                 splits=ctx.attn_splits, hints=ctx, shared_values=True)          # [T, H, R]: weighted latents
+        o = ops.latent_attention(ql, cache.kv, g.block_table, ctx, H, R, n, g.page_size, self.scale)   # [T, H, R]: weighted latents
         out = ops.empty((T, H * e), self.rt.dtype)
         ops.head_linear(o, R, 0, self.w_uv, out, e, 0, H, gate=proj, gate_column=proj.shape[1] - H)    # W_uv[n], times sigmoid(gate n)
         return ops.linear(out, self.w_o)

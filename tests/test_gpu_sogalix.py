@@ -3,6 +3,7 @@
 prompts, decoding, portions, mixed batches, captured steps, generation -- against tests/plain_sogalix.py."""
 import json
 import math
+import random
 import subprocess
 from types import SimpleNamespace
 
@@ -181,7 +182,7 @@ def test_head_norm_with_a_sigmoid_gate_and_a_weight_per_head(ops, dtype, H, d):
 
 # ---------------------------------------------------------------------------- attention with a sink term and a query temperature
 SINK_SHAPES = [   # H, G, d, dv, page, coef, every
-    (6, 1, 48, 48, 16, 0.3, 7), (4, 2, 64, 64, 16, 0.0, 1), (3, 3, 16, 24, 4, 1.0, 1), (8, 2, 128, 128, 8, 0.5, 64), (2, 1, 24, 8, 32, 0.2, 3),
+    (6, 1, 48, 48, 16, 0.3, 7), (4, 2, 64, 64, 16, 0.0, 1), (4, 1, 64, 64, 16, 0.7, 9), (3, 3, 16, 24, 4, 1.0, 1), (8, 2, 128, 128, 8, 0.5, 64), (2, 1, 24, 8, 32, 0.2, 3),
 ]
 
 
@@ -321,3 +322,229 @@ def test_products_per_head_with_and_without_the_gate(ops, dtype, T, H, n_in, n_o
         ops.head_linear(x.cuda(), x_ld, x_ld - n_in, w.cuda(), a, out_ld, 0, H, gate=gate.cuda() if use_gate else None, **kw)
         ref.head_linear(x, x_ld, x_ld - n_in, w, b, out_ld, 0, H, gate=gate if use_gate else None, **kw)
         _close(a, b, dtype, f"gate {use_gate}")
+
+
+# ---------------------------------------------------------------------------- the engine
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    made = {}
+
+    def get(name, dtype, cfg=None, seed=5):
+        if (name, dtype) not in made:
+            folder = tmp_path_factory.mktemp(f"sogalix_{name}_{dtype}")
+            plain.write_model(folder, cfg or plain.TINY[name], seed, DTYPES[dtype])
+            made[(name, dtype)] = folder
+        return made[(name, dtype)]
+    return get
+
+
+def _engine(folder, dtype, page, pages, max_seq_len=512, slots=4, **extra):
+    from pytriton_llama_b200.config import EngineConfig
+    from pytriton_llama_b200.engine.engine import Engine
+    return Engine(folder, EngineConfig(dtype=dtype, page_size=page, max_gpu_num_blocks=pages, max_seq_len=max_seq_len,
+                                       max_num_seqs=slots, **extra), device="cuda:0")
+
+
+def _reference(folder, seqs):
+    from pytriton_llama_b200.weights import read_folder
+    cfg = json.loads((folder / "config.json").read_text())
+    W = read_folder(folder)
+    return {r: plain.forward(cfg, W, s) for r, s in seqs.items()}
+
+
+def _assert_logits(got, ref, dtype, what):
+    diff = (got.double().cpu() - ref).abs()
+    if dtype == "float32":
+        assert diff.max() < TOL32 * max(1.0, float(ref.abs().max())), f"{what}: {diff.max():.3e}"
+    else:       # rounding alone: about 0.01 of the logits' spread in a row
+        centred = (got.double().cpu() - ref) - (got.double().cpu() - ref).mean(-1, keepdim=True)
+        rms = centred.pow(2).mean(-1).sqrt() / ref.std()
+        assert rms.max() < 0.12 and rms.median() < 0.04 + 0.06 * (rms.numel() < 4), \
+            f"{what}: median row {rms.median():.3f}, worst {rms.max():.3f} of the logits' spread"
+
+
+# Wide enough for the tensor-core paths: attention heads of 64 and of 128 with the sink and a temperature that steps
+# inside the prompts, latents of 64 and 128 entries (read by a second layer), delta heads of 64 channels.
+WIDE = plain.config(300, 128, [
+    plain.layer("latent_attention", plain.latent(4, 32, 16, 32, 64, 96, 0.14, 10000.0), plain.dense(192)),
+    plain.layer("general_delta", plain.delta(2, 64), None),
+    plain.layer("attention", plain.attention(4, 2, 64, 64, 0.125, q_temp=(0.5, 48)), plain.dense(64)),
+    plain.layer("latent_attention", plain.latent(2, 64, 16, 64, 64, 48, 0.11, 10000.0, kv_from=0), None),
+    plain.layer("attention", plain.attention(2, 1, 128, 128, 0.09), None),
+    plain.layer("latent_attention", plain.latent(2, 64, 32, 48, 128, 80, 0.1, 500.0), plain.dense(96)),
+])
+
+
+def _config(name):
+    return WIDE if name == "WIDE" else plain.TINY[name]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("C", 16), ("WIDE", 16)])
+def test_every_cut_gives_the_whole_sequence_logits(folders, dtype, name, page):
+    folder = folders(name, dtype, _config(name))
+    vocab = _config(name)["vocab"]
+    seqs = {f"r{i}": random_tokens(n, vocab, 700 + i) for i, n in enumerate([1, 9, 33, 150, 12, 27, 64])}
+    ref = _reference(folder, seqs)
+    for family in (traces.whole, traces.prefill_then_decode, traces.portions, traces.mixed):
+        steps = family(seqs)
+        pages = -(-traces.max_live_tokens(steps, 16) // page)
+        eng = _engine(folder, dtype, page, pages)
+        got = traces.replay(eng, steps)
+        for r in seqs:
+            _assert_logits(got[r], ref[r][traces.wanted_positions(steps, r)], dtype, f"{family.__name__} {r}")
+        eng.check_device_status()
+        assert eng.cache.free_slots() == 4 and all(eng.cache.free_pages(g) == pages for g in eng._paged_groups())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_from_captured_graphs(folders, dtype):
+    folder = folders("WIDE", dtype, WIDE)
+    seqs = {f"g{i}": random_tokens(n, 300, 300 + i) for i, n in enumerate([80, 7, 55, 21, 33])}
+    ref = _reference(folder, seqs)
+    eng = _engine(folder, dtype, 16, 40, compiled_model=True)
+    for turn in range(3):           # the same steps again: shapes seen twice are captured, then replayed
+        for family in (traces.prefill_then_decode, traces.mixed):
+            steps = family(seqs)
+            got = traces.replay(eng, steps)
+            for r in seqs:
+                _assert_logits(got[r], ref[r][traces.wanted_positions(steps, r)], dtype, f"turn {turn} {family.__name__} {r}")
+    assert any(not isinstance(k, tuple) for k in eng._graphs)             # decode steps were captured
+    eng.check_device_status()
+
+
+def _random_config(seed, least_rank=1):
+    """Sizes drawn freely: head sizes that are no power of two, one to three kv heads, ranks from 1 up, rotated parts of
+    2 to 12 entries, temperatures that step every 1 to 40 positions, any order of layers, readers of earlier latents.
+    (A latent of one entry is, after its unit norm, the sign of its input, which rounding to bfloat16 can turn over:
+    the bfloat16 runs ask for ``least_rank`` 5.)"""
+    rng = random.Random(seed)
+    width = rng.choice([24, 40, 64, 72])
+    layers, latents = [], []
+    for i in range(rng.randint(2, 6)):
+        kind = rng.choice(["general_delta", "attention", "latent_attention"])
+        mlp = plain.dense(rng.choice([16, 40, 56])) if rng.random() < 0.6 else None
+        if kind == "general_delta":
+            mixer = plain.delta(rng.randint(1, 4), rng.choice([4, 6, 16, 20, 36]))
+        elif kind == "attention":
+            G = rng.randint(1, 3)
+            mixer = plain.attention(G * rng.randint(1, 3), G, rng.choice([6, 12, 16, 40]), rng.choice([4, 12, 16, 24]), rng.uniform(0.15, 0.5),
+                                    q_temp=(rng.uniform(0.1, 1.0), rng.randint(1, 40)) if rng.random() < 0.7 else None)
+        else:
+            heads, dim, vdim, q_rank = rng.randint(1, 4), rng.choice([4, 10, 16]), rng.choice([6, 8, 20]), max(least_rank, rng.choice([1, 9, 24]))
+            if latents and rng.random() < 0.5:
+                src = rng.choice(latents)
+                m = layers[src]["mixer"]
+                mixer = plain.latent(heads, dim, m["rot_dim"], vdim, m["kv_rank"], q_rank, rng.uniform(0.2, 0.5), m["rot"]["base"], kv_from=src)
+            else:
+                mixer = plain.latent(heads, dim, rng.choice([2, 4, 12]), vdim, max(least_rank, rng.choice([1, 5, 16, 33])), q_rank, rng.uniform(0.2, 0.5),
+                                     rng.choice([10.0, 1000.0, 1e6]))
+                latents.append(i)
+        layers.append(plain.layer(kind, mixer, mlp))
+    return plain.config(rng.choice([33, 101, 260]), width, layers, eps=rng.choice([1e-6, 1e-5, 1e-3]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(10))
+def test_random_configurations(tmp_path, dtype, seed):
+    cfg = _random_config(seed, least_rank=5 if dtype == "bfloat16" else 1)
+    plain.write_model(tmp_path, cfg, seed, DTYPES[dtype])
+    seqs = {f"r{i}": random_tokens(n, cfg["vocab"], 40 * seed + i) for i, n in enumerate([90, 1, 33, 14])}
+    ref = _reference(tmp_path, seqs)
+    page = random.Random(seed).choice([4, 8, 16, 32])
+    for family in (traces.whole, traces.mixed):
+        steps = family(seqs)
+        eng = _engine(tmp_path, dtype, page, -(-traces.max_live_tokens(steps, 32) // page) + 1)
+        got = traces.replay(eng, steps)
+        for r in seqs:
+            _assert_logits(got[r], ref[r][traces.wanted_positions(steps, r)], dtype, f"seed {seed} {family.__name__} {r}")
+        eng.check_device_status()
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_traces_in_float32(folders, seed):
+    folder = folders("A", "float32")
+    rng = random.Random(seed)
+    seqs = {f"t{i}": random_tokens(rng.randint(1, 200), 97, 900 + 10 * seed + i) for i in range(7)}
+    ref = _reference(folder, seqs)
+    steps = traces.random_trace(seqs, rng)
+    for graphs in (False, True):
+        eng = _engine(folder, "float32", 4, -(-traces.max_live_tokens(steps, 4) // 4), compiled_model=graphs)
+        got = traces.replay(eng, steps)
+        for r in got:
+            _assert_logits(got[r], ref[r][traces.wanted_positions(steps, r)], "float32", f"trace {seed} {r}")
+
+
+def test_batch_does_not_change_a_request(folders):
+    from pytriton_llama_b200.engine.engine import StepEntry
+    folder = folders("WIDE", "float32", WIDE)
+    seqs = {"a": random_tokens(137, 300, 1), "b": random_tokens(8, 300, 2), "c": random_tokens(61, 300, 3)}
+    eng = _engine(folder, "float32", 16, 40)
+    together = eng.step([StepEntry(r, s, list(range(len(s)))) for r, s in seqs.items()]).logits
+    eng.finish_all()
+    at = 0
+    for r, s in seqs.items():
+        alone = eng.step([StepEntry(r, s, list(range(len(s))))]).logits
+        eng.finish(r)
+        assert torch.allclose(together[at:at + len(s)], alone, atol=2e-5, rtol=1e-5), r
+        at += len(s)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(folders, dtype):
+    from pytriton_llama_b200.engine.engine import StepEntry
+    folder = folders("WIDE", dtype, WIDE)
+    toks = random_tokens(400, 300, 21)
+    ref = _reference(folder, {"a": toks})["a"]
+    eng = _engine(folder, dtype, 16, 26)
+    rows = [eng.step([StepEntry("a", toks[:3], [0, 1, 2])]).logits] + [eng.step([StepEntry("a", [t], [0])]).logits for t in toks[3:]]
+    _assert_logits(torch.cat(rows), ref, dtype, "400 tokens, one by one")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_scheduler(folders, dtype):
+    from pytriton_llama_b200 import LLM, EngineConfig, SamplingParams
+    folder = folders("A", dtype)
+    prompts = [random_tokens(n, 97, 40 + i) for i, n in enumerate([5, 23, 2, 14, 9, 31])]
+    cfg = EngineConfig(dtype=dtype, page_size=4, max_gpu_num_blocks=60, max_seq_len=64, max_num_seqs=3, max_batched_tokens=16)
+    outs = LLM(folder, cfg).generate(prompts, SamplingParams(temperature=0.0, max_gen_len=8))
+    for p, o in zip(prompts, outs):
+        assert len(o) == 8
+        logits = _reference(folder, {"x": p + o})["x"]
+        slack = 1e-3 if dtype == "float32" else 0.05 * float(logits.std())
+        for i, tok in enumerate(o):
+            row = logits[len(p) + i - 1]
+            assert row[tok] >= row.max() - slack, (i, tok, int(row.argmax()))
+
+
+def test_trace_runner_and_command_line(folders, tmp_path):
+    folder = folders("WIDE", "bfloat16", WIDE)
+    seqs = {"a": random_tokens(90, 300, 1), "b": random_tokens(13, 300, 2)}
+    steps = traces.mixed(seqs)
+    lines = "\n".join(json.dumps(s) for s in steps) + "\n"
+    for dtype in ("bfloat16", "float32"):
+        out = tmp_path / dtype
+        proc = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
+                               "--max-tokens", str(traces.max_live_tokens(steps))], input=lines, text=True, capture_output=True,
+                              timeout=900)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+        ref = _reference(folder, seqs)
+        fed = {r: 0 for r in seqs}
+        got, want = [], []
+        for s in steps:
+            rows = torch.frombuffer(bytearray((out / f"{s['step']}.f32").read_bytes()), dtype=torch.float32).view(-1, 300)
+            at = 0
+            for e in s["entries"]:
+                for w in e["want"]:
+                    got.append(rows[at])
+                    want.append(ref[e["id"]][fed[e["id"]] + w])
+                    at += 1
+                fed[e["id"]] += len(e["tokens"])
+        _assert_logits(torch.stack(got), torch.stack(want), dtype, f"{dtype} replay")
+    import sys
+    proc = subprocess.run([sys.executable, str(ROOT / "cli.py"), "--checkpoints_dir", str(folder), "--temperature", "0",
+                           "--max_gen_len", "5", "--max_seq_len", "64", "--page_size", "16", "--prompt_ids", "3", "1", "4", "1", "5"],
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert len(proc.stdout.split()) == 5

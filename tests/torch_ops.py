@@ -452,6 +452,11 @@ class TorchOps:
         neg = z.clamp(max=0)
         return torch.where(z > 0, pos_factor * z * z + 0.5 * z, neg_factor * (torch.expm1(neg) - neg) + 0.5 * z).to(x.dtype)
 
+    def latent_attention(self, q, cache, block_table, ctx, H, R, n, page_size, scale):
+        """Every head's causal softmax over the kept rows [latent | rotated key part]; the latent is the value."""
+        return self.window_attention(q, cache, block_table, ctx.tok_req, ctx.positions, H, 1, R + n, R, page_size, scale,
+                                     shared_values=True)
+
     def latent_norm_store(self, proj, Q, q_norm, R, kv_norm, n, eps, positions, freq, dims, slots, cache, page_size):
         x = proj.double()
         unit = lambda t: t / torch.sqrt((t * t).mean(-1, keepdim=True) + eps)
