@@ -406,10 +406,19 @@ class CudaOps:
                        float(eps), self._stream()))
         return y, res_out
 
-    def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, fresh_weights: bool = False) -> torch.Tensor:
         """x[T, K] @ w[N, K]^T.  float32: the library's own FFMA kernel (true 32-bit);
         bfloat16: the tensor-core product of this library (a cuBLAS product for sizes it leaves out).
-        ``x`` may be a ``NormedActivation``."""
+        ``x`` may be a ``NormedActivation``.  ``fresh_weights``: ``w`` was written by an earlier kernel of the same
+        step (keys gathered for a product of queries against them).  The tensor-core kernel asks for its first weight
+        tiles before it waits for the kernel ahead of it, which is right for a model's weights only; such a product
+        is therefore launched as an ordinary successor of what runs before it."""
+        if fresh_weights and self.lib.ptl_get_dependent_launch():
+            self.lib.ptl_set_dependent_launch(0)
+            try:
+                return self.linear(x, w, out_dtype)
+            finally:
+                self.lib.ptl_set_dependent_launch(1)
         if isinstance(x, NormedActivation):
             out = self.gemm_tc(x, w, self.EPI_F32 if out_dtype == torch.float32 else self.EPI_BF16)
             if out is not None:
@@ -1324,10 +1333,10 @@ class CudaOps:
                 b = min(qn, a + self.LATENT_QUERY_CHUNK)
                 rows = slice(starts[r] + a, starts[r] + b)
                 n_keys = min(c_pad, -(-(first + b) // 64) * 64)      # no row of the chunk sees a later key
-                scores = self.linear(q[rows].view((b - a) * H, d), keys[:n_keys], out_dtype=torch.float32)
+                scores = self.linear(q[rows].view((b - a) * H, d), keys[:n_keys], out_dtype=torch.float32, fresh_weights=True)
                 weights = self.empty(((b - a) * H, c_pad), q.dtype)
                 self.causal_softmax_rows(weights, scores, ctx.positions, rows.start, H, scale)
-                out[rows] = self.linear(weights, latents_t).view(b - a, H * R)
+                out[rows] = self.linear(weights, latents_t, fresh_weights=True).view(b - a, H * R)
         return out
 
     def latent_gather(self, keys: torch.Tensor, latents_t: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, r: int,

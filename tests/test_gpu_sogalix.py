@@ -40,7 +40,7 @@ def _ctx(q_lens, starts, slots, device):
 def _close(got, ref, dtype, what, scale=None, tol=None):
     got, ref = got.double().cpu(), ref.double().cpu()
     assert got.shape == ref.shape, (what, got.shape, ref.shape)
-    assert torch.isfinite(got).all(), what
+    assert torch.isfinite(got).all(), (what, "not finite at", (~torch.isfinite(got)).nonzero()[:6].tolist(), int((~torch.isfinite(got)).sum()))
     scale = scale or max(1.0, float(ref.abs().max()))
     tol = tol or (2e-5 if dtype == "float32" else 1.2e-2)
     assert (got - ref).abs().max() <= tol * scale, f"{what}: {(got - ref).abs().max():.3e} of {scale:.2f}"
@@ -291,6 +291,34 @@ def test_latent_norms_rotation_and_cache_write(ops, dtype, Q, R, n, dims, extra,
     qa = ops.latent_norm_store(proj.cuda(), Q, wq.cuda(), 0, None, 0, 1e-5, cd.positions, None, 0, None, None, page)
     _close(qa, qb, dtype, "query latent alone")
     assert torch.equal(cu.cpu(), cache)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,R,n,page", [(4, 64, 16, 16), (2, 128, 64, 8), (3, 20, 8, 4), (16, 512, 64, 16), (1, 33, 2, 16)])
+def test_attention_over_the_latents_portions_as_products_and_single_tokens(ops, dtype, H, R, n, page):
+    """Prompts from position 0, portions after a cached prefix (one crossing the query chunk), single tokens and a
+    portion of two, in one step: in bfloat16 the portions go through the gathered rows and two products."""
+    g = torch.Generator().manual_seed(H + R)
+    dt, ref, d = DTYPES[dtype], TorchOps(), R + n
+    q_lens, starts = [150, 1, 70, 1, 2, 600], [0, 90, 121, 0, 130, 37]
+    cd, cc = _ctx(q_lens, starts, [0] * 6, "cuda:0"), _ctx(q_lens, starts, [0] * 6, "cpu")
+    T = sum(q_lens)
+    pages = sum(-(-(s + k) // page) for s, k in zip(starts, q_lens)) + 3
+    bt, _ = _paged(g, q_lens, starts, page, pages, width=-(-640 // page) + 2)
+    q = _rand(g, T, H * d, scale=1.5).to(dt)
+    cache = _rand(g, pages, page * d, scale=0.7).to(dt)
+    hints = ops.hints_for(q_lens, [s + k for s, k in zip(starts, q_lens)])
+    hints.tok_req, hints.positions, hints.attn_splits = cd.tok_req, cd.positions, 1
+    got = ops.latent_attention(q.cuda(), cache.cuda(), bt.cuda(), hints, H, R, n, page, d ** -0.5)
+    want = ref.latent_attention(q, cache, bt, cc, H, R, n, page, d ** -0.5)
+    _close(got, want, dtype, "weighted latents", tol=2e-5 if dtype == "float32" else 2e-2)
+    old = ops.LATENT_QUERY_CHUNK
+    try:            # chunks of 64 tokens: the cut falls inside every longer portion
+        ops.LATENT_QUERY_CHUNK = 64
+        got = ops.latent_attention(q.cuda(), cache.cuda(), bt.cuda(), hints, H, R, n, page, d ** -0.5)
+    finally:
+        ops.LATENT_QUERY_CHUNK = old
+    _close(got, want, dtype, "chunks of 64", tol=2e-5 if dtype == "float32" else 2e-2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
