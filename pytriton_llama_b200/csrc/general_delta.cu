@@ -200,21 +200,54 @@ int general_delta_scan(float* out, const void* proj, int ld, const float* a_pre,
 #undef PTL_GD
 }
 
-// z[t, c] = sum_j w2[c, j] * tanh(x[t, column + j]), float32 throughout, j ascending.  One block per token.
-__global__ void __launch_bounds__(256)
-lowrank_tanh_linear_kernel(float* __restrict__ z, const float* __restrict__ x, int x_ld, int column, int rank,
+// z[t, c] = sum_j w2[c, j] * tanh(x[t, column + j]), float32 throughout.  Every result is one chain of fused
+// multiply-adds, j ascending, whatever the tile it falls into, so a token's row has the same bits in a prompt
+// portion and alone.  A block takes kLtTokens tokens and kLtCols columns: the inner inputs' tanh and a slab of w2
+// (kLtRank values of j at a time, transposed so that neighbouring threads read neighbouring words) go through shared
+// memory; a thread holds one column's sums for all the block's tokens.
+constexpr int kLtTokens = 16, kLtCols = 128, kLtRank = 32;
+
+__global__ void __launch_bounds__(kLtCols)
+lowrank_tanh_linear_kernel(float* __restrict__ z, const float* __restrict__ x, int tokens, int x_ld, int column, int rank,
                            const float* __restrict__ w2, int n) {
-  extern __shared__ float lt_hid[];
+  __shared__ __align__(16) float s_hid[kLtRank][kLtTokens];      // tanh of the inner inputs, tokens side by side
+  __shared__ float s_w[kLtRank][kLtCols + 1];
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
-  for (int jj = threadIdx.x; jj < rank; jj += blockDim.x) lt_hid[jj] = tanhf(x[(size_t)t * x_ld + column + jj]);
-  __syncthreads();
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {
-    const float* wr = w2 + (size_t)c * rank;
-    float acc = 0.f;
-    for (int jj = 0; jj < rank; ++jj) acc = fmaf(wr[jj], lt_hid[jj], acc);
-    z[(size_t)t * n + c] = acc;
+  const int t0 = blockIdx.y * kLtTokens, c0 = blockIdx.x * kLtCols;
+  const int c = c0 + threadIdx.x;
+  float acc[kLtTokens];
+#pragma unroll
+  for (int t = 0; t < kLtTokens; ++t) acc[t] = 0.f;
+  for (int j0 = 0; j0 < rank; j0 += kLtRank) {
+    const int nj = min(kLtRank, rank - j0);
+    __syncthreads();                                               // the slab before has been used
+    for (int e = threadIdx.x; e < kLtTokens * kLtRank; e += kLtCols) {
+      const int t = e / kLtRank, jj = e % kLtRank;
+      s_hid[jj][t] = (t0 + t < tokens && jj < nj) ? tanhf(x[(size_t)(t0 + t) * x_ld + column + j0 + jj]) : 0.f;
+    }
+    for (int e = threadIdx.x; e < kLtCols * kLtRank; e += kLtCols) {
+      const int cc = e / kLtRank, jj = e % kLtRank;
+      s_w[jj][cc] = (c0 + cc < n && jj < nj) ? w2[(size_t)(c0 + cc) * rank + j0 + jj] : 0.f;
+    }
+    __syncthreads();
+    for (int jj = 0; jj < nj; ++jj) {
+      const float w = s_w[jj][threadIdx.x];
+      const float4* hp = reinterpret_cast<const float4*>(s_hid[jj]);
+#pragma unroll
+      for (int q = 0; q < kLtTokens / 4; ++q) {
+        const float4 hv = hp[q];
+        acc[4 * q + 0] = fmaf(w, hv.x, acc[4 * q + 0]);
+        acc[4 * q + 1] = fmaf(w, hv.y, acc[4 * q + 1]);
+        acc[4 * q + 2] = fmaf(w, hv.z, acc[4 * q + 2]);
+        acc[4 * q + 3] = fmaf(w, hv.w, acc[4 * q + 3]);
+      }
+    }
+  }
+  if (c < n) {
+#pragma unroll
+    for (int t = 0; t < kLtTokens; ++t)
+      if (t0 + t < tokens) z[(size_t)(t0 + t) * n + c] = acc[t];
   }
 }
 
@@ -222,11 +255,13 @@ lowrank_tanh_linear_kernel(float* __restrict__ z, const float* __restrict__ x, i
 
 PTL_EXPORT int ptl_lowrank_tanh_linear(float* z, const float* x, int tokens, int x_ld, int column, int rank, const float* w2, int n,
                                        void* stream) {
-  PTL_REQUIRE(tokens >= 0 && rank > 0 && n > 0 && column >= 0 && column + rank <= x_ld && rank <= 8192,
+  PTL_REQUIRE(tokens >= 0 && rank > 0 && n > 0 && column >= 0 && column + rank <= x_ld,
               "lowrank_tanh_linear: bad sizes rank=%d n=%d column=%d ld=%d", rank, n, column, x_ld);
   if (tokens == 0) return 0;
-  return ptl::launch_kernel("lowrank_tanh_linear", ptl::lowrank_tanh_linear_kernel, dim3(tokens), dim3(256),
-                            (size_t)rank * sizeof(float), ptl::as_stream(stream), z, x, x_ld, column, rank, w2, n);
+  const dim3 grid((n + ptl::kLtCols - 1) / ptl::kLtCols, (tokens + ptl::kLtTokens - 1) / ptl::kLtTokens);
+  PTL_REQUIRE(grid.y <= 65535, "lowrank_tanh_linear: %d tokens in one call", tokens);
+  return ptl::launch_kernel("lowrank_tanh_linear", ptl::lowrank_tanh_linear_kernel, grid, dim3(ptl::kLtCols), 0,
+                            ptl::as_stream(stream), z, x, tokens, x_ld, column, rank, w2, n);
 }
 
 #define PTL_GENERAL_DELTA(SUFFIX, TYPE)                                                                                          \

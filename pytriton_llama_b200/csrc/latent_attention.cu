@@ -186,6 +186,30 @@ int causal_softmax_rows(void* weights, int ld_out, const float* scores, long lon
                        (T*)weights, ld_out, scores, n_keys, positions, heads, scale, sink);
 }
 
+// out[t, h * ld + col + c] *= sigmoid(gate[t * gate_ld + h]), c < n (float32 inside, rounded once): the heads' gates on a
+// result that a batched product of the library wrote.  One block per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_gate_kernel(T* __restrict__ out, int ld, int col, int n, int heads, const T* __restrict__ gate, int gate_ld) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t t = blockIdx.x;
+  for (int idx = threadIdx.x; idx < heads * n; idx += blockDim.x) {
+    const int h = idx / n, c = idx % n;
+    const float g = 1.0f / (1.0f + expf(-to_f32(gate[t * gate_ld + h])));
+    T* o = out + t * (size_t)heads * ld + (size_t)h * ld + col + c;
+    *o = from_f32<T>(to_f32(*o) * g);
+  }
+}
+
+template <typename T>
+int head_gate(void* out, int ld, int col, int n, int tokens, int heads, const void* gate, int gate_ld, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && heads > 0 && n > 0 && col >= 0 && col + n <= ld && gate && gate_ld >= heads, "head_gate: bad sizes");
+  if (tokens == 0) return 0;
+  return launch_kernel("head_gate", head_gate_kernel<T>, dim3(tokens), dim3(256), 0, as_stream(stream), (T*)out, ld, col, n, heads,
+                       (const T*)gate, gate_ld);
+}
+
 }  // namespace ptl
 
 #define PTL_LATENT(SUFFIX, TYPE)                                                                                                  \
@@ -198,6 +222,10 @@ int causal_softmax_rows(void* weights, int ld_out, const float* scores, long lon
   PTL_EXPORT int ptl_rotate_head_part##SUFFIX(void* out, int out_ld, int out_col, const void* x, int x_ld, int x_col, int tokens,  \
                                               int heads, int n, const int* positions, const float* freq, int dims, void* stream) { \
     return ptl::rotate_head_part<TYPE>(out, out_ld, out_col, x, x_ld, x_col, tokens, heads, n, positions, freq, dims, stream);     \
+  }                                                                                                                               \
+  PTL_EXPORT int ptl_head_gate##SUFFIX(void* out, int ld, int col, int n, int tokens, int heads, const void* gate, int gate_ld,    \
+                                       void* stream) {                                                                            \
+    return ptl::head_gate<TYPE>(out, ld, col, n, tokens, heads, gate, gate_ld, stream);                                           \
   }
 #define PTL_LATENT_PREFILL(SUFFIX, TYPE)                                                                                          \
   PTL_EXPORT int ptl_latent_gather##SUFFIX(void* keys, void* latents_t, const void* cache, const int* bt, int ctx, int c_pad,      \

@@ -63,23 +63,39 @@ int add_layernorm(void* y, float* residual_out, const float* residual_in, const 
                        residual_out, residual_in, (const TX*)x, add_bias, w, b, rows, hidden, eps);
 }
 
+__device__ __forceinline__ float xielu_f32(float z, float ap, float aq) {
+  return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z);
+}
+
+// A thread takes one packet of 16 bytes (PER elements); the elements after the last whole packet go one by one.
 template <typename T>
-__global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ x, long long n, float ap, float aq) {
+__global__ void __launch_bounds__(256) xielu_kernel(T* __restrict__ out, const T* __restrict__ x, long long n, long long packets,
+                                                    float ap, float aq) {
+  constexpr int PER = 16 / sizeof(T);
   pdl_wait();
   pdl_launch_dependents();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  const float z = to_f32(x[i]);
-  const float v = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z);
-  out[i] = from_f32<T>(v);
+  if (i < packets) {
+    uint4 raw = reinterpret_cast<const uint4*>(x)[i];
+    T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int e = 0; e < PER; ++e) v[e] = from_f32<T>(xielu_f32(to_f32(v[e]), ap, aq));
+    reinterpret_cast<uint4*>(out)[i] = raw;
+  } else {
+    const long long j = packets * PER + (i - packets);
+    if (j < n) out[j] = from_f32<T>(xielu_f32(to_f32(x[j]), ap, aq));
+  }
 }
 
 template <typename T>
 int xielu(void* out, const void* x, long long n, float ap, float aq, void* stream) {
   PTL_REQUIRE(n >= 0, "xielu: bad size");
   if (n == 0) return 0;
-  return launch_kernel("xielu", xielu_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, as_stream(stream), (T*)out,
-                       (const T*)x, n, ap, aq);
+  constexpr int PER = 16 / sizeof(T);
+  const long long packets = (aligned16(out) && aligned16(x)) ? n / PER : 0;
+  const long long threads = packets + (n - packets * PER);
+  return launch_kernel("xielu", xielu_kernel<T>, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, as_stream(stream), (T*)out,
+                       (const T*)x, n, packets, ap, aq);
 }
 
 }  // namespace ptl

@@ -56,6 +56,7 @@ _SIGNATURES = {
     "ptl_latent_norm_store": [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr, _c_int, _c_f, _ptr, _ptr, _c_int, _ptr, _ptr,
                               _c_ll, _ptr],
     "ptl_rotate_head_part": [_ptr, _c_int, _c_int, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr],
+    "ptl_head_gate": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr],
     "ptl_latent_gather": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr],
     "ptl_causal_softmax_rows": [_ptr, _c_int, _ptr, _c_ll, _c_int, _ptr, _c_int, _c_f, _c_int, _ptr],
     "ptl_head_linear": [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr],
@@ -276,7 +277,7 @@ class CudaOps:
         "stream_mix_norm": "norm", "gelu_tanh": "elementwise", "qk_norm_rotate_store": "rope", "window_attention": "attention",
         "gla_scan": "recurrent", "routed_experts": "experts",
         "add_layernorm": "norm", "xielu": "elementwise", "lowrank_tanh_linear": "recurrent", "general_delta_scan": "recurrent",
-        "latent_norm_store": "rope", "rotate_head_part": "rope", "head_linear": "product",
+        "latent_norm_store": "rope", "rotate_head_part": "rope", "head_linear": "product", "head_gate": "elementwise",
         "latent_gather": "attention", "causal_softmax_rows": "attention",
     }
 
@@ -1367,6 +1368,8 @@ class CudaOps:
         self._check(fn(_p(weights), weights.shape[1], _p(scores), rows, n_keys, positions.data_ptr() + 4 * first_token, H,
                        float(scale), int(bool(sink)), self._stream()))
 
+    HEAD_PRODUCT_MIN_TOKENS = int(os.environ.get("PTL_HEAD_PRODUCT_MIN", "128"))     # tokens from which the heads' products go to the library
+
     def head_linear(self, x: torch.Tensor, x_ld: int, x_col: int, w: torch.Tensor, out: torch.Tensor, out_ld: int, out_col: int,
                     H: int, gate: Optional[torch.Tensor] = None, gate_column: int = 0) -> None:
         """For every head h: out[:, h*out_ld + out_col + o] = sum_i x[:, h*x_ld + x_col + i] * w[h, o, i], with ``gate``
@@ -1381,6 +1384,22 @@ class CudaOps:
         if gate is not None:
             self._want(gate, "gate", x.dtype)
             gate_ptr = gate.data_ptr() + gate_column * gate.element_size()
+        T = x.shape[0]
+        if x.dtype == torch.bfloat16 and T >= self.HEAD_PRODUCT_MIN_TOKENS and self.library_products:
+            # many tokens: one batched product of the library on the tensor cores (float32 sums), the operands
+            # and the result addressed in place by their strides; the heads' gates by a kernel of their own
+            a = x.view(T, H, x_ld)[:, :, x_col:x_col + n_in].transpose(0, 1)            # [H, T, n_in]
+            o = out.view(T, H, out_ld)[:, :, out_col:out_col + n_out].transpose(0, 1)    # [H, T, n_out]
+            matmul = torch.backends.cuda.matmul
+            before = matmul.allow_bf16_reduced_precision_reduction
+            matmul.allow_bf16_reduced_precision_reduction = False
+            try:
+                torch.bmm(a, w.transpose(1, 2), out=o)
+            finally:
+                matmul.allow_bf16_reduced_precision_reduction = before
+            if gate is not None:
+                self._check(self.lib.ptl_head_gate_bf16(_p(out), out_ld, out_col, n_out, T, H, gate_ptr, gate.shape[1], self._stream()))
+            return
         fn = getattr(self.lib, "ptl_head_linear" + _suffix(x.dtype))
         self._check(fn(out.data_ptr() + out_col * out.element_size(), x.data_ptr() + x_col * x.element_size(), _p(w), x.shape[0],
                        n_out, n_in, x.shape[1], out.shape[1], H, x_ld, out_ld, gate_ptr, gate.shape[1] if gate is not None else 0,

@@ -109,6 +109,18 @@ def _delta_inputs(g, T, H, d, dt, rank=5):
     return proj, aw, _rand(g, n), _rand(g, n, rank), 2 * torch.rand(n, generator=g) - 1
 
 
+@pytest.mark.parametrize("T,n,rank,extra", [(1, 7, 3, 0), (16, 128, 32, 5), (17, 129, 33, 4), (70, 300, 70, 1), (5, 1000, 64, 8)])
+def test_decay_argument_tiles_and_single_rows(ops, T, n, rank, extra):
+    g = torch.Generator().manual_seed(T + n + rank)
+    aw, w2 = _rand(g, T, extra + rank, scale=1.5), _rand(g, n, rank)
+    za = ops.lowrank_tanh_linear(aw.cuda(), extra, w2.cuda())
+    _close(za, TorchOps().lowrank_tanh_linear(aw, extra, w2), "float32", "decay argument")
+    # a row alone has the bits it has inside a tile
+    t = T // 2
+    alone = ops.lowrank_tanh_linear(aw[t:t + 1].contiguous().cuda(), extra, w2.cuda())
+    assert torch.equal(alone[0], za[t])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,d", [(3, 32), (2, 20), (1, 128), (2, 200), (4, 4), (1, 64), (5, 8), (1, 40)])
 def test_delta_walk_and_its_state(ops, dtype, H, d):
