@@ -25,13 +25,41 @@ namespace ptl {
 template <typename T>
 __global__ void __launch_bounds__(256)
 latent_gather_kernel(T* __restrict__ keys, T* __restrict__ latents_t, const T* __restrict__ cache, const int* __restrict__ bt,
-                     int ctx, int c_pad, int d, int R, int page_size, int num_pages) {
+                     int ctx, int c_pad, int d, int R, int page_size, int num_pages, int vec_ok) {
   extern __shared__ __align__(16) unsigned char lg_raw[];
   T* tile = reinterpret_cast<T*>(lg_raw);          // [32][d + 2]
   pdl_wait();
   pdl_launch_dependents();
   const int ld = d + 2;
   const int k0 = blockIdx.x * 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (vec_ok) {
+    // 16-bit entries, rows of whole packets of 16 bytes: a packet per load, four words per store into the tile (its rows
+    // start on 4-byte boundaries only); then two keys of one latent entry per store, 16 lanes a row of the tile
+    const int ppr = d / 8;
+    for (int idx = threadIdx.x; idx < 32 * ppr; idx += blockDim.x) {
+      const int row = idx / ppr, pk = idx % ppr;
+      const int key = k0 + row;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (key < ctx) {
+        const int page = bt[key / page_size];
+        if (page >= 0 && page < num_pages)
+          v = reinterpret_cast<const uint4*>(cache + ((size_t)page * page_size + key % page_size) * d)[pk];
+      }
+      unsigned* tw = reinterpret_cast<unsigned*>(tile + row * ld + 8 * pk);
+      tw[0] = v.x; tw[1] = v.y; tw[2] = v.z; tw[3] = v.w;
+      if (key < c_pad) reinterpret_cast<uint4*>(keys + (size_t)key * d)[pk] = v;
+    }
+    __syncthreads();
+    const int q = lane & 15, half = lane >> 4;
+    if (k0 + 2 * q + 1 < c_pad) {
+      for (int e = 2 * warp + half; e < R; e += 16) {
+        T two[2] = {tile[(2 * q) * ld + e], tile[(2 * q + 1) * ld + e]};
+        *reinterpret_cast<unsigned*>(latents_t + (size_t)e * c_pad + k0 + 2 * q) = *reinterpret_cast<unsigned*>(two);
+      }
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < 32 * d; idx += blockDim.x) {
     const int row = idx / d, e = idx % d;
     const int key = k0 + row;
@@ -44,7 +72,6 @@ latent_gather_kernel(T* __restrict__ keys, T* __restrict__ latents_t, const T* _
     if (key < c_pad) keys[(size_t)key * d + e] = v;
   }
   __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (k0 + lane < c_pad)
     for (int e = warp; e < R; e += 8) latents_t[(size_t)e * c_pad + k0 + lane] = tile[lane * ld + e];
 }
@@ -54,7 +81,8 @@ latent_gather_kernel(T* __restrict__ keys, T* __restrict__ latents_t, const T* _
 template <typename T>
 __global__ void __launch_bounds__(256)
 causal_softmax_rows_kernel(T* __restrict__ weights, int ld_out, const float* __restrict__ scores, int n_keys,
-                           const int* __restrict__ positions, int heads, float scale, int sink) {
+                           const int* __restrict__ positions, int heads, float scale, int sink, int held) {
+  extern __shared__ __align__(16) float sr_row[];     // held: the row's scaled scores, then its exponentials
   __shared__ float red[33];
   pdl_wait();
   pdl_launch_dependents();
@@ -64,6 +92,39 @@ causal_softmax_rows_kernel(T* __restrict__ weights, int ld_out, const float* __r
   const float* s = scores + row * (size_t)n_keys;
   T* w = weights + row * (size_t)ld_out;
   float m = sink ? 0.f : -INFINITY;
+  if (held) {
+    // n_keys and ld_out are multiples of 4 and the row fits shared memory: the scores are read once, four at a time, and
+    // every exponential is worked out once.  A thread meets the same j in every pass.
+    const int n4 = (n + 3) & ~3;
+    for (int j = 4 * threadIdx.x; j < n4; j += 4 * blockDim.x) {
+      float4 v = *reinterpret_cast<const float4*>(s + j);
+      v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+      if (j + 1 >= n) v.y = -INFINITY;
+      if (j + 2 >= n) v.z = -INFINITY;
+      if (j + 3 >= n) v.w = -INFINITY;
+      *reinterpret_cast<float4*>(sr_row + j) = v;
+      m = fmaxf(m, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+    }
+    m = block_max(m, red);
+    float sum = 0.f;
+    for (int j = 4 * threadIdx.x; j < n4; j += 4 * blockDim.x) {
+      float4 v = *reinterpret_cast<const float4*>(sr_row + j);
+      v.x = expf(v.x - m); v.y = expf(v.y - m); v.z = expf(v.z - m); v.w = expf(v.w - m);     // exp(-inf) = 0 beyond n
+      *reinterpret_cast<float4*>(sr_row + j) = v;
+      sum += (v.x + v.y) + (v.z + v.w);
+    }
+    sum = block_sum(sum, red);
+    if (sink) sum += expf(-m);
+    const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+    for (int j = 4 * threadIdx.x; j < ld_out; j += 4 * blockDim.x) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j < n4) v = *reinterpret_cast<const float4*>(sr_row + j);
+      T o[4] = {from_f32<T>(v.x * inv), from_f32<T>(v.y * inv), from_f32<T>(v.z * inv), from_f32<T>(v.w * inv)};
+      if (sizeof(T) == 2) *reinterpret_cast<uint2*>(w + j) = *reinterpret_cast<uint2*>(o);
+      else *reinterpret_cast<uint4*>(w + j) = *reinterpret_cast<uint4*>(o);
+    }
+    return;
+  }
   for (int j = threadIdx.x; j < n; j += blockDim.x) m = fmaxf(m, s[j] * scale);
   m = block_max(m, red);
   float sum = 0.f;
@@ -173,8 +234,10 @@ int latent_gather(void* keys, void* latents_t, const void* cache, const int* bt,
   const size_t smem = (size_t)32 * (d + 2) * sizeof(T);
   PTL_REQUIRE(smem <= 48 * 1024, "latent_gather: rows of %d entries do not fit shared memory", d);
   if (c_pad == 0) return 0;
+  const int vec_ok = sizeof(T) == 2 && d % 8 == 0 && c_pad % 2 == 0 && aligned16(keys) && aligned16(cache) &&
+                     (reinterpret_cast<uintptr_t>(latents_t) & 3u) == 0;
   return launch_kernel("latent_gather", latent_gather_kernel<T>, dim3((c_pad + 31) / 32), dim3(256), smem, as_stream(stream),
-                       (T*)keys, (T*)latents_t, (const T*)cache, bt, ctx, c_pad, d, R, page_size, num_pages);
+                       (T*)keys, (T*)latents_t, (const T*)cache, bt, ctx, c_pad, d, R, page_size, num_pages, vec_ok);
 }
 
 template <typename T>
@@ -182,8 +245,11 @@ int causal_softmax_rows(void* weights, int ld_out, const float* scores, long lon
                         int heads, float scale, int sink, void* stream) {
   PTL_REQUIRE(rows >= 0 && rows < (1ll << 31) && n_keys > 0 && ld_out >= n_keys && heads > 0, "causal_softmax_rows: bad sizes");
   if (rows == 0) return 0;
-  return launch_kernel("causal_softmax_rows", causal_softmax_rows_kernel<T>, dim3((unsigned)rows), dim3(256), 0, as_stream(stream),
-                       (T*)weights, ld_out, scores, n_keys, positions, heads, scale, sink);
+  const int held = n_keys % 4 == 0 && ld_out % 4 == 0 && (size_t)n_keys * sizeof(float) <= 40 * 1024 && aligned16(scores) &&
+                   aligned16(weights);
+  return launch_kernel("causal_softmax_rows", causal_softmax_rows_kernel<T>, dim3((unsigned)rows), dim3(256),
+                       held ? (size_t)n_keys * sizeof(float) : 0, as_stream(stream), (T*)weights, ld_out, scores, n_keys, positions,
+                       heads, scale, sink, held);
 }
 
 // out[t, h * ld + col + c] *= sigmoid(gate[t * gate_ld + h]), c < n (float32 inside, rounded once): the heads' gates on a

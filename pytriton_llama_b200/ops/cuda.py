@@ -277,7 +277,7 @@ class CudaOps:
         "stream_mix_norm": "norm", "gelu_tanh": "elementwise", "qk_norm_rotate_store": "rope", "window_attention": "attention",
         "gla_scan": "recurrent", "routed_experts": "experts",
         "add_layernorm": "norm", "xielu": "elementwise", "lowrank_tanh_linear": "recurrent", "general_delta_scan": "recurrent",
-        "latent_norm_store": "rope", "rotate_head_part": "rope", "head_linear": "product", "head_gate": "elementwise",
+        "latent_norm_store": "rope", "rotate_head_part": "rope", "head_linear": "product",
         "latent_gather": "attention", "causal_softmax_rows": "attention",
     }
 
