@@ -151,6 +151,85 @@ int gemm_simt(void* out, const void* A, const void* W, int M, int N, int K, int 
   }
 }
 
+// The heads' products of a step with few tokens, 16-bit operands: a warp per output feature o of a head reads the weight
+// row W[b, o, :] once, in packets of 16 bytes, against up to kHfTok token rows held as float32 in shared memory;
+// float32 sums, each (token, feature) by the same chain whatever else the step holds: a lane adds its packets in order,
+// the lanes meet in a butterfly.  K a multiple of 8, every row on a 16-byte boundary.
+constexpr int kHfTok = 8, kHfWarps = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(kHfWarps * 32)
+head_linear_few_kernel(T* __restrict__ out, const T* __restrict__ A, const T* __restrict__ W, int M, int N, int K, int lda, int ldo,
+                       int batch_a, int batch_o, const T* __restrict__ gate, int gate_ld) {
+  extern __shared__ __align__(16) float hf_x[];          // [kHfTok][K]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.y, m0 = blockIdx.z * kHfTok;
+  const int nt = min(kHfTok, M - m0);
+  const int packets = K / 8;
+  for (int idx = threadIdx.x; idx < kHfTok * packets; idx += blockDim.x) {
+    const int t = idx / packets, pk = idx % packets;
+    float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+    if (t < nt) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(A + (size_t)(m0 + t) * lda + (size_t)b * batch_a + 8 * pk);
+      const T* v = reinterpret_cast<const T*>(&raw);
+      lo = make_float4(to_f32(v[0]), to_f32(v[1]), to_f32(v[2]), to_f32(v[3]));
+      hi = make_float4(to_f32(v[4]), to_f32(v[5]), to_f32(v[6]), to_f32(v[7]));
+    }
+    float4* dst = reinterpret_cast<float4*>(hf_x + (size_t)t * K + 8 * pk);
+    dst[0] = lo;
+    dst[1] = hi;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int o = blockIdx.x * kHfWarps + warp;
+  if (o >= N) return;
+  const T* wr = W + ((size_t)b * N + o) * K;
+  float acc[kHfTok];
+#pragma unroll
+  for (int t = 0; t < kHfTok; ++t) acc[t] = 0.f;
+  for (int i = lane * 8; i < K; i += 256) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(wr + i);
+    const T* v = reinterpret_cast<const T*>(&raw);
+    float w[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w[e] = to_f32(v[e]);
+#pragma unroll
+    for (int t = 0; t < kHfTok; ++t) {
+      const float4* xp = reinterpret_cast<const float4*>(hf_x + (size_t)t * K + i);
+      const float4 x0 = xp[0], x1 = xp[1];
+      float a = acc[t];
+      a = fmaf(w[0], x0.x, a); a = fmaf(w[1], x0.y, a); a = fmaf(w[2], x0.z, a); a = fmaf(w[3], x0.w, a);
+      a = fmaf(w[4], x1.x, a); a = fmaf(w[5], x1.y, a); a = fmaf(w[6], x1.z, a); a = fmaf(w[7], x1.w, a);
+      acc[t] = a;
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kHfTok; ++t) {
+    const float v = warp_sum(acc[t]);
+    if (lane == t && t < nt) {
+      const size_t m = (size_t)(m0 + t);
+      const float g = gate ? 1.0f / (1.0f + expf(-to_f32(gate[m * gate_ld + b]))) : 1.0f;
+      out[m * ldo + (size_t)b * batch_o + o] = from_f32<T>(v * g);
+    }
+  }
+}
+
+template <typename T>
+int head_linear_few(void* out, const void* A, const void* W, int M, int N, int K, int lda, int ldo, int heads, int batch_a,
+                    int batch_o, const void* gate, int gate_ld, void* stream) {
+  PTL_REQUIRE(M >= 0 && N > 0 && K > 0 && heads >= 1 && heads <= 65535, "head_linear_few: bad sizes M=%d N=%d K=%d", M, N, K);
+  PTL_REQUIRE(sizeof(T) == 2 && K % 8 == 0 && lda % 8 == 0 && batch_a % 8 == 0 && aligned16(A) && aligned16(W) &&
+                  (size_t)kHfTok * K * sizeof(float) <= 48 * 1024,
+              "head_linear_few: 16-bit rows of whole packets of 16 bytes on 16-byte boundaries, K=%d at most 1536", K);
+  if (M == 0) return 0;
+  const dim3 grid((N + kHfWarps - 1) / kHfWarps, heads, (M + kHfTok - 1) / kHfTok);
+  PTL_REQUIRE(grid.z <= 65535, "head_linear_few: M=%d too large", M);
+  return launch_kernel("head_linear_few", head_linear_few_kernel<T>, grid, dim3(kHfWarps * 32), (size_t)kHfTok * K * sizeof(float),
+                       as_stream(stream), (T*)out, (const T*)A, (const T*)W, M, N, K, lda, ldo, batch_a, batch_o, (const T*)gate,
+                       gate_ld);
+}
+
 }  // namespace ptl
 
 PTL_EXPORT int ptl_gemm_simt_f32(void* out, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldo, int accumulate, void* stream) {
@@ -173,4 +252,8 @@ PTL_EXPORT int ptl_head_linear_bf16(void* out, const void* A, const void* W, int
                                     int batch_a, int batch_o, const void* gate, int gate_ld, void* stream) {
   return ptl::gemm_simt<__nv_bfloat16, __nv_bfloat16>(out, A, W, M, N, K, lda, K, ldo, 0, stream, heads, batch_a, (long long)N * K,
                                                       batch_o, gate, gate_ld);
+}
+PTL_EXPORT int ptl_head_linear_few_bf16(void* out, const void* A, const void* W, int M, int N, int K, int lda, int ldo, int heads,
+                                        int batch_a, int batch_o, const void* gate, int gate_ld, void* stream) {
+  return ptl::head_linear_few<__nv_bfloat16>(out, A, W, M, N, K, lda, ldo, heads, batch_a, batch_o, gate, gate_ld, stream);
 }

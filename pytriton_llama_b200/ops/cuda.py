@@ -174,6 +174,8 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_moe_grouped_wide_bf16.restype = _c_int
     lib.ptl_lowrank_tanh_linear.argtypes = [_ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr]
     lib.ptl_lowrank_tanh_linear.restype = _c_int
+    lib.ptl_head_linear_few_bf16.argtypes = _SIGNATURES["ptl_head_linear"]
+    lib.ptl_head_linear_few_bf16.restype = _c_int
     lib.ptl_last_error.restype = ctypes.c_char_p
     lib.ptl_set_dependent_launch.argtypes = [_c_int]
     lib.ptl_get_dependent_launch.restype = _c_int
@@ -1368,6 +1370,7 @@ class CudaOps:
         self._check(fn(_p(weights), weights.shape[1], _p(scores), rows, n_keys, positions.data_ptr() + 4 * first_token, H,
                        float(scale), int(bool(sink)), self._stream()))
 
+    HEAD_FEW_MAX_TOKENS = int(os.environ.get("PTL_HEAD_FEW_MAX", "16"))              # tokens up to which the heads' products take the row-per-warp kernel
     HEAD_PRODUCT_MIN_TOKENS = int(os.environ.get("PTL_HEAD_PRODUCT_MIN", "128"))     # tokens from which the heads' products go to the library
 
     def head_linear(self, x: torch.Tensor, x_ld: int, x_col: int, w: torch.Tensor, out: torch.Tensor, out_ld: int, out_col: int,
@@ -1401,6 +1404,9 @@ class CudaOps:
                 self._check(self.lib.ptl_head_gate_bf16(_p(out), out_ld, out_col, n_out, T, H, gate_ptr, gate.shape[1], self._stream()))
             return
         fn = getattr(self.lib, "ptl_head_linear" + _suffix(x.dtype))
+        if (x.dtype == torch.bfloat16 and T <= self.HEAD_FEW_MAX_TOKENS and n_in % 8 == 0 and n_in <= 1536 and x_ld % 8 == 0
+                and x_col % 8 == 0 and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            fn = self.lib.ptl_head_linear_few_bf16          # few tokens: a warp per output feature reads its weight row once
         self._check(fn(out.data_ptr() + out_col * out.element_size(), x.data_ptr() + x_col * x.element_size(), _p(w), x.shape[0],
                        n_out, n_in, x.shape[1], out.shape[1], H, x_ld, out_ld, gate_ptr, gate.shape[1] if gate is not None else 0,
                        self._stream()))

@@ -348,7 +348,7 @@ def test_rotation_of_one_part_of_every_head(ops, dtype, H, d, n, R, dims):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T", [1, 7, 150])
+@pytest.mark.parametrize("T", [1, 7, 13, 40, 150])
 @pytest.mark.parametrize("H,n_in,n_out,x_ld,out_ld", [(3, 16, 20, 24, 28), (4, 64, 64, 96, 96), (1, 8, 12, 32, 36), (5, 6, 6, 10, 10),
                                                      (2, 128, 512, 192, 576), (2, 512, 128, 512, 128), (6, 20, 24, 20, 24)])
 def test_products_per_head_with_and_without_the_gate(ops, dtype, T, H, n_in, n_out, x_ld, out_ld):
