@@ -9,6 +9,12 @@ tokens, pages are taken when a step needs them and given back when a request end
 windowed group, when the window has passed them (but for the pages of the first positions where
 those stay visible); the bookkeeping lives on the host.
 
+An entry whose need names a ``pool_block`` of P positions also belongs to a second group of kind
+"summary": its pages hold one mean key and one mean value per complete block of P positions of a
+request, in the layout of the entry's own pages.  A request holds ceil(floor(tokens / P) / page_size) of
+them until it ends; the slot of a token in that group is where the mean of the block that the token
+completes goes, -1 for a token that completes none.
+
 Cache entries (one per run of a layer that stores keys and values) with equal needs form a
 group.  A page id is valid in every entry of its group: entry e keeps its share of page p in
 ``kv[e][p]`` of shape [2 (k, v), kv_heads, page_size, head_dim].
@@ -150,6 +156,7 @@ class CacheManager:
         self.dtype = dtype
         self.groups: List[CacheGroup] = []
         self.entry_group: Dict[int, int] = {}
+        self.entry_summary_group: Dict[int, int] = {}      # entries that keep block means -> their "summary" group
         by_key: Dict[Tuple, int] = {}
         for e in sorted(entries):
             need = entries[e]
@@ -161,10 +168,23 @@ class CacheManager:
             g = by_key[key]
             self.groups[g].entries.append(e)
             self.entry_group[e] = g
+            if need.pool_block > 0 and self.groups[g].paged:
+                skey = ("summary",) + tuple(key)
+                if skey not in by_key:
+                    by_key[skey] = len(self.groups)
+                    sneed = CacheNeed(kind="summary", kv_heads=need.kv_heads, head_dim=need.head_dim, window=need.pool_block,
+                                      value_dim=need.value_dim)
+                    self.groups.append(CacheGroup(sneed, [], page_size, PagePool(self.summary_pages(num_pages, need.pool_block))))
+                self.groups[by_key[skey]].entries.append(e)
+                self.entry_summary_group[e] = by_key[skey]
         if allocate:
             for grp in self.groups:
                 n = grp.need
                 for e in grp.entries:
+                    if grp.paged and n.kind == "summary":
+                        grp.kv[e] = torch.zeros((grp.pool.num_pages, n.kv_heads * page_size * (n.head_dim + n.stored_v_dim)),
+                                                dtype=dtype, device=self.device)
+                        continue
                     if grp.paged and n.stored_v_dim == n.head_dim:
                         grp.kv[e] = torch.zeros((num_pages, 2, n.kv_heads, page_size, n.head_dim),
                                                 dtype=dtype, device=self.device)
@@ -180,6 +200,18 @@ class CacheManager:
                                                    dtype=n.state_dtype or torch.float32, device=self.device)
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
         self._requests: Dict[Hashable, _Request] = {}
+
+    def summary_pages(self, num_pages: int, block: int) -> int:
+        """Pages of block means that go with ``num_pages`` pages of tokens: what the requests can hold when the pages
+        of tokens bound them (each request wastes up to one page), and never more than every request at full length."""
+        most = self.max_requests * -(-(self.max_seq_len // block) // self.page_size)
+        return max(1, min(most, -(-num_pages // block) + self.max_requests))
+
+    def _blocks_for(self, grp: CacheGroup, tokens: int) -> int:
+        """Pages of ``grp`` that a request of ``tokens`` tokens has taken so far (given back or not)."""
+        if grp.need.kind == "summary":
+            tokens //= grp.need.window
+        return -(-tokens // self.page_size)
 
     # ------------------------------------------------------------------ queries
     def has(self, req: Hashable) -> bool:
@@ -234,11 +266,11 @@ class CacheManager:
             r = None
             have = have_tokens or 0
         out = {}
-        total_blocks = -(-(have + new_tokens) // self.page_size)
         for gi, grp in enumerate(self.groups):
             if not grp.paged:
                 continue
-            held = len(r.tables[gi]) if r else -(-have // self.page_size)
+            total_blocks = self._blocks_for(grp, have + new_tokens)
+            held = len(r.tables[gi]) if r else self._blocks_for(grp, have)
             need = total_blocks - held
             if r is not None and grp.need.kind in ("window", "chunk"):
                 need -= r.tables[gi].held_below(self._first_needed_block(grp, have), self._kept_blocks(grp))
@@ -289,12 +321,23 @@ class CacheManager:
             if not grp.paged:
                 continue
             table = r.tables[gi]
+            if grp.need.kind == "summary":
+                P = grp.need.window
+                done = (r.tokens + new_tokens) // P
+                if -(-done // ps) > len(table):
+                    table.extend(grp.pool.take(-(-done // ps) - len(table)))
+                pos = np.arange(r.tokens, r.tokens + new_tokens)
+                block = (pos + 1) // P - 1                    # the block that a position completes, if it is its last
+                last = (pos + 1) % P == 0
+                pages = table.pages[np.where(last, block, 0) // ps].astype(np.int64) if len(table) else np.zeros_like(pos)
+                out[gi] = np.where(last, pages * ps + block % ps, -1).tolist()
+                continue
             first = self._first_needed_block(grp, r.tokens)
             for b in range(self._kept_blocks(grp), min(first, len(table))):
                 if table[b] >= 0:
                     grp.pool.give_back(table[b])
                     table[b] = -1
-            total_blocks = -(-(r.tokens + new_tokens) // ps)
+            total_blocks = self._blocks_for(grp, r.tokens + new_tokens)
             if total_blocks > len(table):
                 table.extend(grp.pool.take(total_blocks - len(table)))
             if new_tokens == 1:

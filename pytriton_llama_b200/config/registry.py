@@ -61,6 +61,9 @@ def _register_builtin() -> None:
     from .sogalix import SogalixConfig
     from ..models.sogalix import sogalix_spec
     register_architecture("Sogalix", SogalixConfig.from_dict, sogalix_spec)
+    from .podizen import PodizenConfig
+    from ..models.podizen import podizen_spec
+    register_architecture("Podizen", PodizenConfig.from_dict, podizen_spec)
 
 
 _register_builtin()

@@ -1,6 +1,9 @@
 // Gated linear attention: per head a float32 state S [d, dv] that decays per key channel,
 //   S <- diag(a_t) S + k_t v_t^T,   o_t = S^T q_t,   a_t = sigmoid(z_t + b)^(1/tau) = exp(logsigmoid(z_t + b) / tau).
 //
+// With `head_decay` (and no z) every key channel of head h decays by the fixed head_decay[h] instead (retention);
+// `k_scale` multiplies the keys.
+//
 // proj is the projection's output [T, q | k | v | ...] (H heads of d, d, dv), z float32 [T, H*d] before
 // the bias.  A block owns 32 columns of one head's state for one request and walks the request's
 // tokens of this step in order.  The 32 lanes of a warp are the 32 columns; each of the 8 warps holds
@@ -27,7 +30,8 @@ template <typename T, int RPL, int TB>   // RPL rows per lane (d <= 8 * RPL), TB
 __global__ void __launch_bounds__(kGlaThreads)
 gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, const float* __restrict__ z,
                 const float* __restrict__ bias, float inv_tau, float* __restrict__ state, const int* __restrict__ q_start,
-                const int* __restrict__ positions, const int* __restrict__ state_slot, int H, int d, int dv, float q_scale) {
+                const int* __restrict__ positions, const int* __restrict__ state_slot, int H, int d, int dv, float q_scale,
+                const float* __restrict__ head_decay, float k_scale) {
   constexpr int DP = kGlaLanes * RPL;
   __shared__ __align__(16) float s_q[TB][DP], s_k[TB][DP], s_a[TB][DP];
   __shared__ float s_v[TB][kGlaCols];
@@ -59,7 +63,8 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, con
   constexpr int kTokStep = kGlaThreads / DP > 0 ? kGlaThreads / DP : 1;
   static_assert(kGlaThreads % DP == 0 && NE * kTokStep == TB, "a thread's column must not change between its turns");
   const int c_mine = tid % DP, j_mine = tid / DP;
-  const float b_mine = c_mine < d ? bias[qcol + c_mine] : 0.f;
+  const float b_mine = (z && c_mine < d) ? bias[qcol + c_mine] : 0.f;
+  const float fixed = head_decay ? head_decay[h] : 0.f;
   T rq[NE], rk[NE], rv[NV];
   float rz[NE];
   auto fetch = [&](int tb) {
@@ -71,7 +76,7 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, con
       const T* row = proj + (size_t)(tb + (ok ? j : 0)) * ld;
       rq[i] = ok ? row[qcol + c_mine] : from_f32<T>(0.f);
       rk[i] = ok ? row[kcol + c_mine] : from_f32<T>(0.f);
-      rz[i] = ok ? z[(size_t)(tb + j) * H * d + qcol + c_mine] : 0.f;
+      rz[i] = (ok && z) ? z[(size_t)(tb + j) * H * d + qcol + c_mine] : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -85,8 +90,8 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, con
     for (int i = 0; i < NE; ++i) {
       const int j = j_mine + i * kTokStep;
       s_q[j][c_mine] = to_f32(rq[i]) * q_scale;
-      s_k[j][c_mine] = to_f32(rk[i]);
-      s_a[j][c_mine] = c_mine < d ? expf(log_sigmoid_f32(rz[i] + b_mine) * inv_tau) : 0.f;
+      s_k[j][c_mine] = to_f32(rk[i]) * k_scale;
+      s_a[j][c_mine] = c_mine < d ? (z ? expf(log_sigmoid_f32(rz[i] + b_mine) * inv_tau) : fixed) : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -146,8 +151,9 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, con
 template <typename T>
 int gla_scan(float* out, const void* proj, int ld, const float* z, const float* bias, float inv_tau, float* state,
              const int* q_start, const int* positions, const int* state_slot, int requests, int H, int d, int dv,
-             float q_scale, void* stream) {
+             float q_scale, const float* head_decay, float k_scale, void* stream) {
   PTL_REQUIRE(requests >= 0 && H > 0 && d > 0 && dv > 0, "gla_scan: bad sizes");
+  PTL_REQUIRE((z && bias) || head_decay, "gla_scan: neither a decay per channel nor one per head");
   PTL_REQUIRE(d <= 256, "gla_scan: head size %d, at most 256", d);
   PTL_REQUIRE(ld >= 2 * H * d + H * dv, "gla_scan: rows of %d elements are too short", ld);
   PTL_REQUIRE(H <= 65535 && requests <= 65535, "gla_scan: too many heads or requests");
@@ -155,7 +161,7 @@ int gla_scan(float* out, const void* proj, int ld, const float* z, const float* 
   const dim3 grid((dv + kGlaCols - 1) / kGlaCols, H, requests), block(kGlaThreads);
 #define PTL_GLA_LAUNCH(RPL, TB)                                                                                              \
   return launch_kernel("gla_scan", gla_scan_kernel<T, RPL, TB>, grid, block, 0, as_stream(stream), out, (const T*)proj, ld, z, \
-                       bias, inv_tau, state, q_start, positions, state_slot, H, d, dv, q_scale)
+                       bias, inv_tau, state, q_start, positions, state_slot, H, d, dv, q_scale, z ? nullptr : head_decay, k_scale)
   if (d <= 32) PTL_GLA_LAUNCH(4, 16);
   if (d <= 64) PTL_GLA_LAUNCH(8, 16);
   if (d <= 128) PTL_GLA_LAUNCH(16, 16);
@@ -168,9 +174,10 @@ int gla_scan(float* out, const void* proj, int ld, const float* z, const float* 
 #define PTL_GLA(SUFFIX, TYPE)                                                                                                   \
   PTL_EXPORT int ptl_gla_scan##SUFFIX(float* out, const void* proj, int ld, const float* z, const float* bias, float inv_tau,    \
                                       float* state, const int* q_start, const int* positions, const int* state_slot,            \
-                                      int requests, int H, int d, int dv, float q_scale, void* stream) {                        \
+                                      int requests, int H, int d, int dv, float q_scale, const float* head_decay,               \
+                                      float k_scale, void* stream) {                                                            \
     return ptl::gla_scan<TYPE>(out, proj, ld, z, bias, inv_tau, state, q_start, positions, state_slot, requests, H, d, dv,       \
-                               q_scale, stream);                                                                                \
+                               q_scale, head_decay, k_scale, stream);                                                           \
   }
 PTL_GLA(_f32, float)
 PTL_GLA(_bf16, __nv_bfloat16)

@@ -2,7 +2,10 @@
 // device, grouped products over tiles of tokens of one expert each, combine.
 //
 //   moe_route     one warp per token: score = sigmoid(logit) in float32, the `top` largest scores (the
-//                 lower index wins a tie), expert ids and scores out.
+//                 lower index wins a tie), expert ids and scores out.  Options: score = softmax(logit) over
+//                 all experts; `groups` > 1: experts form that many groups of neighbours, a group's score is
+//                 its largest score and only experts of the `keep` best groups can be chosen (the lower group
+//                 wins a tie); `renorm`: the chosen scores are divided by their sum + 1e-20.
 //   moe_plan      one block: tokens per expert, each expert's rows padded to whole tiles of kMoeTile rows,
 //                 the list of tiles (expert, first row, rows), the row of every (token, choice).
 //   moe_gather    sorted[row] = x[token] (* score when the weight multiplies the expert's input), rounded to T.
@@ -29,23 +32,68 @@ __device__ __forceinline__ float moe_silu(float x) { return x / (1.0f + expf(-x)
 // ------------------------------------------------------------------ route
 __global__ void __launch_bounds__(128)
 moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ logits, int tokens, int E,
-                 int top) {
+                 int top, int softmax, int groups, int keep, int renorm) {
+  __shared__ float s_best[4][kMoeMaxExperts];      // per warp: the largest score of every group
   pdl_wait();
   pdl_launch_dependents();
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
   if (t >= tokens) return;
   constexpr int kPerLane = kMoeMaxExperts / 32;
   float sc[kPerLane];
+  float zmax = -INFINITY;
 #pragma unroll
   for (int i = 0; i < kPerLane; ++i) {
     const int e = lane + 32 * i;
     float v = -INFINITY;
     if (e < E) {
-      v = sigmoid_f32(logits[(size_t)t * E + e]);
+      v = logits[(size_t)t * E + e];
       if (!(v == v)) v = -INFINITY;        // a NaN never wins
+      if (!softmax) v = sigmoid_f32(v);
     }
     sc[i] = v;
+    zmax = fmaxf(zmax, v);
+  }
+  if (softmax) {
+    zmax = warp_max(zmax);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      if (lane + 32 * i < E) {
+        sc[i] = sc[i] > -INFINITY ? expf(sc[i] - zmax) : 0.f;
+        sum += sc[i];
+      }
+    }
+    sum = warp_sum(sum);
+    const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i)
+      if (lane + 32 * i < E) sc[i] *= inv;
+  }
+  if (groups > 1 && keep < groups) {
+    const int per = E / groups;
+    float* best_of = s_best[warp];
+    for (int gi = lane; gi < groups; gi += 32) best_of[gi] = -INFINITY;
+    __syncwarp();
+    // an expert's group is e / per; lanes hold experts 32 apart, so the groups' maxima are taken through shared memory
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E) atomicMax(reinterpret_cast<int*>(&best_of[e / per]), __float_as_int(fmaxf(sc[i], 0.f)));   // scores are >= 0: their bit patterns order as they do
+    }
+    __syncwarp();
+    // a group is kept if fewer than `keep` groups beat it (a larger score, or the same score and a lower number)
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E) {
+        const int mine = e / per;
+        const float b = best_of[mine];
+        int ahead = 0;
+        for (int gi = 0; gi < groups; ++gi) ahead += (best_of[gi] > b || (best_of[gi] == b && gi < mine)) ? 1 : 0;
+        if (ahead >= keep) sc[i] = -INFINITY;
+      }
+    }
   }
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
@@ -66,6 +114,13 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i)
       if (lane + 32 * i == best_e) sc[i] = -INFINITY;
+  }
+  if (renorm) {
+    __syncwarp();                          // lane 0's weights, read back by all
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) sum += weights[(size_t)t * top + k];       // in the order they were chosen, the same in every lane
+    const float inv = 1.0f / (sum + 1e-20f);
+    for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= inv;
   }
 }
 
@@ -592,11 +647,14 @@ moe_combine_kernel(float* __restrict__ out, const float* __restrict__ C, const T
 }
 
 // ------------------------------------------------------------------ launchers
-int moe_route(int* ids, float* weights, const float* logits, int tokens, int E, int top, void* stream) {
+int moe_route(int* ids, float* weights, const float* logits, int tokens, int E, int top, int softmax, int groups, int keep,
+              int renorm, void* stream) {
   PTL_REQUIRE(tokens >= 0 && E >= 1 && E <= kMoeMaxExperts && top >= 1 && top <= E, "moe_route: %d experts, top %d (at most %d experts)", E, top, kMoeMaxExperts);
+  PTL_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups && top <= keep * (E / groups),
+              "moe_route: %d experts in %d groups, %d kept, top %d", E, groups, keep, top);
   if (tokens == 0) return 0;
   return launch_kernel("moe_route", moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, as_stream(stream), ids, weights, logits,
-                       tokens, E, top);
+                       tokens, E, top, softmax, groups, keep, renorm);
 }
 
 int moe_plan(int* pos, int* tiles, int* meta, const int* ids, int n, int E, int max_tiles, int* wide, int max_wide, void* stream) {
@@ -658,8 +716,9 @@ int moe_combine(float* out, const float* C, const void* shared_out, const int* p
 }  // namespace ptl
 
 PTL_EXPORT int ptl_moe_tile_rows() { return ptl::kMoeTile; }
-PTL_EXPORT int ptl_moe_route(int* ids, float* weights, const float* logits, int tokens, int E, int top, void* stream) {
-  return ptl::moe_route(ids, weights, logits, tokens, E, top, stream);
+PTL_EXPORT int ptl_moe_route(int* ids, float* weights, const float* logits, int tokens, int E, int top, int softmax, int groups,
+                             int keep, int renorm, void* stream) {
+  return ptl::moe_route(ids, weights, logits, tokens, E, top, softmax, groups, keep, renorm, stream);
 }
 PTL_EXPORT int ptl_moe_wide_rows() { return ptl::kMoeWide; }
 PTL_EXPORT int ptl_moe_plan(int* pos, int* tiles, int* meta, const int* ids, int n, int E, int max_tiles, int* wide, int max_wide,

@@ -21,7 +21,19 @@
 // whose longer portions another kernel takes); partial results are indexed by the row itself.
 // Options: `sink` adds one term of score 0 (and no value) to the softmax's denominator; `temp_coef` != 0
 // multiplies the scores of the query at position p by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1);
-// `shared_v`: pages hold keys only and the value of a key is its first dv entries.
+// `shared_v`: pages hold keys only and the value of a key is its first dv entries.  `bias_exp` = c > 0: head h takes
+// 2^(-c (h + 1) / H) * (p - j) off the score of key j.  `gate_col` >= 0: the result of head h is multiplied by the
+// sigmoid of the dv entries at column gate_col + h * dv of the token's q row.  `pool` = P > 0 (with a window): the list
+// starts with one mean key and mean value for every block b of P positions with bP + P - 1 <= p - window, read from
+// `summary`, pages of the cache's layout with a block table of their own; that part of the list is padded to whole
+// turns of 32 so that a turn reads either means or tokens.
+//
+// head_norm_rotate_store, per token, on [T, q | k | v | ...]: every q and k head divided by its own root mean square
+// and multiplied by the weight [d] of its kind (eps > 0), entries i and i + rot/2 of a head turned by
+// float(position) * inv_freq[i]; in place, k and v to the token's slot.  A warp per head.
+//
+// pool_blocks, per token with a slot in `summary`: the mean over the P positions that end with the token's own of
+// the keys and of the values in the cache, added in ascending order of position and divided by P.
 #include "common.cuh"
 
 namespace ptl {
@@ -194,6 +206,137 @@ int qk_norm_rotate_store(void* proj, int tokens, int ld, int H, int G, int d, in
                        G > 0 ? slots : nullptr, (T*)cache, page_size, num_slots, vec_ok);
 }
 
+// ------------------------------------------------------------------ per-head norm + rotation of halves + cache write
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_norm_rotate_store_kernel(T* __restrict__ proj, int ld, int H, int G, int d, int dv, const float* __restrict__ wq,
+                              const float* __restrict__ wk, float eps, const int* __restrict__ positions,
+                              const float* __restrict__ inv_freq, int rot, const int* __restrict__ slots, T* __restrict__ cache,
+                              int page_size, long long num_slots) {
+  extern __shared__ float hn_smem[];       // cos[rot/2], sin[rot/2], then d floats per warp
+  const int t = blockIdx.x;
+  const int half = rot / 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  float* cs = hn_smem;
+  float* sn = hn_smem + half;
+  float* buf = hn_smem + 2 * half + warp * d;
+  const float pos = (float)positions[t];   // an input of the step, not a result of the kernel before
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], sn + j, cs + j);
+  pdl_wait();
+  pdl_launch_dependents();
+  __syncthreads();
+  T* row = proj + (size_t)t * ld;
+  long long slot = (slots && cache) ? (long long)slots[t] : -1;
+  if (slot >= num_slots) slot = -1;
+  const size_t page_stride = (size_t)G * page_size * (d + dv);
+  T* kdst = nullptr;
+  T* vdst = nullptr;
+  if (slot >= 0) {
+    const size_t page = (size_t)(slot / page_size), off = (size_t)(slot % page_size);
+    kdst = cache + page * page_stride + off * d;                                  // + g * page_size * d
+    vdst = cache + page * page_stride + (size_t)G * page_size * d + off * dv;     // + g * page_size * dv
+  }
+  for (int h = warp; h < H + G; h += nwarps) {
+    T* src = row + (size_t)h * d;
+    const bool is_k = h >= H;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      const float v = to_f32(src[i]);
+      buf[i] = v;
+      ss = fmaf(v, v, ss);
+    }
+    float r = 1.f;
+    if (eps > 0.f) r = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+    __syncwarp();
+    const float* w = eps > 0.f ? (is_k ? wk : wq) : nullptr;
+    T* kd = (is_k && kdst) ? kdst + (size_t)(h - H) * page_size * d : nullptr;
+    for (int i = lane; i < d; i += 32) {
+      float x = buf[i] * r * (w ? w[i] : 1.f);
+      if (i < rot) {
+        const int j = i < half ? i : i - half;
+        const int other = i < half ? i + half : i - half;
+        const float xo = buf[other] * r * (w ? w[other] : 1.f);
+        x = i < half ? fmaf(x, cs[j], -xo * sn[j]) : fmaf(x, cs[j], xo * sn[j]);
+      }
+      const T o = from_f32<T>(x);
+      src[i] = o;
+      if (kd) kd[i] = o;
+    }
+    __syncwarp();
+  }
+  if (vdst) {
+    const T* v = row + (size_t)(H + G) * d;
+    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+      const int g = i / dv, e = i % dv;
+      vdst[(size_t)g * page_size * dv + e] = v[i];
+    }
+  }
+}
+
+template <typename T>
+int head_norm_rotate_store(void* proj, int tokens, int ld, int H, int G, int d, int dv, const float* wq, const float* wk, float eps,
+                           const int* positions, const float* inv_freq, int rot, const int* slots, void* cache, int page_size,
+                           long long num_slots, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && H > 0 && G >= 0 && d > 0 && dv > 0 && page_size > 0, "head_norm_rotate_store: bad sizes");
+  PTL_REQUIRE(ld >= (H + G) * d + G * dv, "head_norm_rotate_store: rows of %d elements are too short", ld);
+  PTL_REQUIRE(eps <= 0.f || (wq && (G == 0 || wk)), "head_norm_rotate_store: the norm needs its weights");
+  PTL_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d && (rot == 0 || inv_freq), "head_norm_rotate_store: rotary width %d of head size %d", rot, d);
+  PTL_REQUIRE(d <= 4096, "head_norm_rotate_store: head size %d", d);
+  if (tokens == 0) return 0;
+  const size_t smem = ((size_t)rot + 8 * (size_t)d) * sizeof(float);
+  static SmemRaised raised;
+  if (smem > 48 * 1024)
+    if (int rc = raise_shared_memory("head_norm_rotate_store", head_norm_rotate_store_kernel<T>, 200 * 1024, raised)) return rc;
+  return launch_kernel("head_norm_rotate_store", head_norm_rotate_store_kernel<T>, dim3(tokens), dim3(256), smem, as_stream(stream),
+                       (T*)proj, ld, H, G, d, dv, wq, wk, eps, positions, rot > 0 ? inv_freq : nullptr, rot,
+                       G > 0 ? slots : nullptr, (T*)cache, page_size, num_slots);
+}
+
+// ------------------------------------------------------------------ means of whole blocks
+template <typename T>
+__global__ void __launch_bounds__(128)
+pool_blocks_kernel(T* __restrict__ summary, const T* __restrict__ cache, const int* __restrict__ block_table,
+                   const int* __restrict__ tok_req, const int* __restrict__ positions, const int* __restrict__ sum_slots,
+                   int bt_stride, int G, int d, int dv, int page_size, int block, int num_pages, long long num_sum_slots) {
+  const int t = blockIdx.x;
+  const long long sl = sum_slots[t];       // inputs of the step
+  const int r = tok_req[t], p = positions[t];
+  pdl_wait();
+  pdl_launch_dependents();
+  if (sl < 0 || sl >= num_sum_slots || r < 0 || p + 1 < block) return;
+  const size_t page_stride = (size_t)G * page_size * (d + dv);
+  const size_t v_plane = (size_t)G * page_size * d;
+  const int* bt = block_table + (size_t)r * bt_stride;
+  T* dst = summary + (size_t)(sl / page_size) * page_stride;
+  const int off = (int)(sl % page_size);
+  const float inv = 1.0f / (float)block;
+  for (int idx = threadIdx.x; idx < G * (d + dv); idx += blockDim.x) {
+    const bool is_v = idx >= G * d;
+    const int g = is_v ? (idx - G * d) / dv : idx / d;
+    const int e = is_v ? (idx - G * d) % dv : idx % d;
+    const int wd = is_v ? dv : d;
+    const size_t plane = is_v ? v_plane : 0;
+    float acc = 0.f;
+    for (int j = p - block + 1; j <= p; ++j) {
+      const int page = bt[j / page_size];
+      if (page < 0 || page >= num_pages) continue;        // never follow a table entry outside the pool
+      acc += to_f32(cache[(size_t)page * page_stride + plane + ((size_t)g * page_size + j % page_size) * wd + e]);
+    }
+    dst[plane + ((size_t)g * page_size + off) * wd + e] = from_f32<T>(acc * inv);
+  }
+}
+
+template <typename T>
+int pool_blocks(void* summary, const void* cache, const int* block_table, const int* tok_req, const int* positions,
+                const int* sum_slots, int tokens, int bt_stride, int G, int d, int dv, int page_size, int block, int num_pages,
+                long long num_sum_slots, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && G > 0 && d > 0 && dv > 0 && page_size > 0 && block > 0 && num_pages > 0, "pool_blocks: bad sizes");
+  if (tokens == 0) return 0;
+  return launch_kernel("pool_blocks", pool_blocks_kernel<T>, dim3(tokens), dim3(128), 0, as_stream(stream), (T*)summary,
+                       (const T*)cache, block_table, tok_req, positions, sum_slots, bt_stride, G, d, dv, page_size, block,
+                       num_pages, num_sum_slots);
+}
+
 // ------------------------------------------------------------------ attention
 constexpr int kWaMaxPerLane = 16;  // value heads up to 512 (kernels are built for 8 and for 16 values per lane)
 constexpr int kWaWarps = 4;
@@ -223,7 +366,8 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
                         const int* __restrict__ tok_req, const int* __restrict__ positions, int q_stride, int out_stride,
                         int bt_stride, int H, int G, int d, int dv, int page_size, float scale, int window, int keep,
                         int splits, int num_pages, int vec_ok, const int* __restrict__ items, int wide_ok, int shared_v,
-                        int sink, float temp_coef, int temp_every) {
+                        int sink, float temp_coef, int temp_every, float bias_exp, int gate_col, int pool,
+                        const T* __restrict__ summary, const int* __restrict__ sum_bt, int sum_bt_stride, int sum_pages) {
   constexpr int kWaMaxPerLane = MPL;   // values of a head that a lane holds
   extern __shared__ float qs_all[];  // [warps][d]
   __shared__ float s_pr[kWaWarps][32];
@@ -246,7 +390,10 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
 
   const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int n_keep = min(keep, lo);                 // kept positions that the window has passed
-  const int n_list = r < 0 ? 0 : n_keep + (p - lo + 1);
+  const int n_pool = (pool > 0 && window > 0 && r >= 0 && p - window + 1 > 0) ? (p - window + 1) / pool : 0;   // whole blocks behind the window
+  const int n_pool_pad = (n_pool + 31) & ~31;
+  const int n_list = r < 0 ? 0 : n_pool_pad + n_keep + (p - lo + 1);
+  const float slope = bias_exp > 0.f ? exp2f(-bias_exp * (float)(h + 1) / (float)H) : 0.f;
   int chunk = (n_list + splits - 1) / splits;
   chunk = (chunk + 31) & ~31;
   const int i_begin = split * chunk;
@@ -256,6 +403,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
   const size_t v_plane = shared_v ? 0 : (size_t)G * page_size * d;
   const int v_row = shared_v ? d : dv;      // elements between the values of neighbouring keys
   const int* bt = block_table + (size_t)(r < 0 ? 0 : r) * bt_stride;
+  const int* sbt = sum_bt ? sum_bt + (size_t)(r < 0 ? 0 : r) * sum_bt_stride : nullptr;
   constexpr int VN = Vec16<T>::N;
 
   float m = -INFINITY, l = 0.f, l_lo = 0.f;
@@ -266,15 +414,19 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
   for (int i0 = i_begin; i0 < i_end; i0 += 32) {
     const int li = i0 + lane;
     bool valid = li < i_end;
-    const int key = li < n_keep ? li : lo + (li - n_keep);
-    size_t vbase = 0;
+    const bool mean = li < n_pool_pad;                  // the same for all lanes of a turn
+    if (mean && li >= n_pool) valid = false;
+    const int lt = li - n_pool_pad;
+    const int key = mean ? li : (lt < n_keep ? lt : lo + (lt - n_keep));     // a block's number, or a position
+    const T* vptr = cache + v_plane;
     float s = -INFINITY;
-    const int page = valid ? bt[key / page_size] : 0;
-    if (page < 0 || page >= num_pages) valid = false;   // never follow a table entry outside the pool
+    const int page = valid ? (mean ? sbt[key / page_size] : bt[key / page_size]) : 0;
+    if (page < 0 || page >= (mean ? sum_pages : num_pages)) valid = false;   // never follow a table entry outside the pool
     if (valid) {
       const size_t in_page = (size_t)g * page_size + key % page_size;
-      const T* kp = cache + (size_t)page * page_stride + in_page * d;
-      vbase = (size_t)page * page_stride + v_plane + in_page * v_row;
+      const T* pg = (mean ? summary : cache) + (size_t)page * page_stride;
+      const T* kp = pg + in_page * d;
+      vptr = pg + v_plane + in_page * v_row;
       float dot = 0.f, dot_lo = 0.f;
       if (vec_ok) {
         // four packets of the key row are requested together and used afterwards: a product right behind its load
@@ -302,6 +454,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
         }
       }
       s = kCompensated ? __fadd_rn(dot, dot_lo) * scale : dot;
+      if (!mean) s = fmaf(-slope, (float)(p - key), s);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float pr = valid ? expf(s - m_new) : 0.f;
@@ -324,7 +477,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
     // address of the cache's first value row)
     __syncwarp();
     s_pr[warp][lane] = pr;
-    s_vb[warp][lane] = valid ? (unsigned long long)vbase : (unsigned long long)v_plane;
+    s_vb[warp][lane] = (unsigned long long)vptr;
     __syncwarp();
     const int nvalid = min(32, i_end - i0);
     // (lanes past the list's end hold weight 0 and the address of a value row that exists, so the walks below take
@@ -337,7 +490,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
         uint2 raw[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-          const T* vp = cache + (size_t)s_vb[warp][j0 + u] + lane * wide_ok;
+          const T* vp = reinterpret_cast<const T*>(s_vb[warp][j0 + u]) + lane * wide_ok;
           if (wide_ok == 4) raw[u] = *reinterpret_cast<const uint2*>(vp);
           else raw[u].x = *reinterpret_cast<const uint32_t*>(vp);
         }
@@ -359,7 +512,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
         T raw[4][kWaMaxPerLane];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const T* vp = cache + (size_t)s_vb[warp][j0 + u];
+          const T* vp = reinterpret_cast<const T*>(s_vb[warp][j0 + u]);
 #pragma unroll
           for (int i = 0; i < kWaMaxPerLane; ++i) {
             const int dd = lane + 32 * i;
@@ -396,10 +549,15 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
     }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     T* o = out + (size_t)t * out_stride + (size_t)h * dv;
+    const T* gate = gate_col >= 0 ? q + (size_t)t * q_stride + gate_col + (size_t)h * dv : nullptr;
 #pragma unroll
     for (int i = 0; i < kWaMaxPerLane; ++i) {
       const int dd = wide_ok ? lane * wide_ok + i : lane + 32 * i;
-      if (dd < dv && (!wide_ok || i < wide_ok)) o[dd] = from_f32<T>(acc[i] * inv);
+      if (dd < dv && (!wide_ok || i < wide_ok)) {
+        float res = acc[i] * inv;
+        if (gate) res *= 1.0f / (1.0f + expf(-to_f32(gate[dd])));
+        o[dd] = from_f32<T>(res);
+      }
     }
   } else {
     const size_t idx = ((size_t)t * H + h) * splits + split;
@@ -417,7 +575,8 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
 template <typename T, int MPL>
 __global__ void __launch_bounds__(kWaWarps * 32)
 window_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                              int out_stride, int H, int dv, int splits, int tokens, const int* __restrict__ items, int sink) {
+                              int out_stride, int H, int dv, int splits, int tokens, const int* __restrict__ items, int sink,
+                              const T* __restrict__ q, int q_stride, int gate_col) {
   constexpr int kWaMaxPerLane = MPL;
   pdl_wait();
   pdl_launch_dependents();
@@ -476,10 +635,15 @@ window_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ par
   if (sink) L += expf(-M);
   const float inv = L > 0.f ? 1.0f / L : 0.f;
   T* o = out + (size_t)t * out_stride + (size_t)h * dv;
+  const T* gate = gate_col >= 0 ? q + (size_t)t * q_stride + gate_col + (size_t)h * dv : nullptr;
 #pragma unroll
   for (int i = 0; i < kWaMaxPerLane; ++i) {
     const int dd = lane + 32 * i;
-    if (dd < dv) o[dd] = from_f32<T>(acc[i] * inv);
+    if (dd < dv) {
+      float res = acc[i] * inv;
+      if (gate) res *= 1.0f / (1.0f + expf(-to_f32(gate[dd])));
+      o[dd] = from_f32<T>(res);
+    }
   }
 }
 
@@ -487,8 +651,13 @@ template <typename T>
 int window_attention(void* out, const void* q, const void* cache, const int* block_table, const int* tok_req,
                      const int* positions, float* part_acc, float* part_ml, int tokens, int q_stride, int out_stride,
                      int bt_stride, int H, int G, int d, int dv, int page_size, float scale, int window, int keep, int splits,
-                     int num_pages, const int* items, int shared_v, int sink, float temp_coef, int temp_every, void* stream) {
+                     int num_pages, const int* items, int shared_v, int sink, float temp_coef, int temp_every, float bias_exp,
+                     int gate_col, int pool, const void* summary, const int* sum_bt, int sum_bt_stride, int sum_pages,
+                     void* stream) {
   PTL_REQUIRE(tokens >= 0 && H > 0 && G > 0 && page_size > 0 && d > 0, "window_attention: bad sizes");
+  PTL_REQUIRE(pool == 0 || (summary && sum_bt && sum_pages > 0 && window > 0 && keep == 0 && !shared_v && !sink),
+              "window_attention: means of blocks need their pages and a window, and go with no kept positions, shared values or sink");
+  PTL_REQUIRE(bias_exp >= 0.f && (gate_col < 0 || gate_col + H * dv <= q_stride), "window_attention: bad bias or gate column");
   PTL_REQUIRE(!shared_v || dv <= d, "window_attention: values of %d entries inside keys of %d", dv, d);
   PTL_REQUIRE(temp_every >= 1, "window_attention: temp_every=%d", temp_every);
   PTL_REQUIRE(H % G == 0, "window_attention: %d query heads are no multiple of %d kv heads", H, G);
@@ -515,11 +684,13 @@ int window_attention(void* out, const void* q, const void* cache, const int* blo
     int rc = launch_kernel("window_attention", window_attention_kernel<T, MPL>, grid, dim3(kWaWarps * 32), smem,                   \
                            as_stream(stream), (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req,      \
                            positions, q_stride, out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits,        \
-                           num_pages, vec_ok, items, wide_ok, shared_v, sink, temp_coef, temp_every);                              \
+                           num_pages, vec_ok, items, wide_ok, shared_v, sink, temp_coef, temp_every, bias_exp, gate_col, pool,     \
+                           (const T*)summary, sum_bt, sum_bt_stride, sum_pages);                                                  \
     if (rc || splits <= 1) return rc;                                                                                              \
     return launch_kernel("window_attention_merge", window_attention_merge_kernel<T, MPL>,                                          \
                          dim3((unsigned)((pairs + kWaWarps - 1) / kWaWarps)), dim3(kWaWarps * 32), 0, as_stream(stream), (T*)out,  \
-                         (const float*)part_acc, (const float*)part_ml, out_stride, H, dv, splits, tokens, items, sink);           \
+                         (const float*)part_acc, (const float*)part_ml, out_stride, H, dv, splits, tokens, items, sink,            \
+                         (const T*)q, q_stride, gate_col);                                                                         \
   }
   if (dv <= 32 * 8) PTL_WA_LAUNCH(8)      // (value heads up to 256 keep the registers of 8 values per lane)
   PTL_WA_LAUNCH(16)
@@ -541,10 +712,25 @@ int window_attention(void* out, const void* q, const void* cache, const int* blo
                                               int tokens, int q_stride, int out_stride, int bt_stride, int H, int G, int d, int dv, \
                                               int page_size, float scale, int window, int keep, int splits, int num_pages,         \
                                               const int* items, int shared_v, int sink, float temp_coef, int temp_every,           \
-                                              void* stream) {                                                                      \
+                                              float bias_exp, int gate_col, int pool, const void* summary, const int* sum_bt,      \
+                                              int sum_bt_stride, int sum_pages, void* stream) {                                    \
     return ptl::window_attention<TYPE>(out, q, cache, block_table, tok_req, positions, part_acc, part_ml, tokens, q_stride,        \
                                        out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages,      \
-                                       items, shared_v, sink, temp_coef, temp_every, stream);                                      \
+                                       items, shared_v, sink, temp_coef, temp_every, bias_exp, gate_col, pool, summary, sum_bt,    \
+                                       sum_bt_stride, sum_pages, stream);                                                          \
+  }                                                                                                                                \
+  PTL_EXPORT int ptl_head_norm_rotate_store##SUFFIX(void* proj, int tokens, int ld, int H, int G, int d, int dv, const float* wq,   \
+                                                    const float* wk, float eps, const int* positions, const float* inv_freq,       \
+                                                    int rot, const int* slots, void* cache, int page_size, long long num_slots,    \
+                                                    void* stream) {                                                                \
+    return ptl::head_norm_rotate_store<TYPE>(proj, tokens, ld, H, G, d, dv, wq, wk, eps, positions, inv_freq, rot, slots, cache,    \
+                                             page_size, num_slots, stream);                                                        \
+  }                                                                                                                                \
+  PTL_EXPORT int ptl_pool_blocks##SUFFIX(void* summary, const void* cache, const int* block_table, const int* tok_req,              \
+                                         const int* positions, const int* sum_slots, int tokens, int bt_stride, int G, int d,      \
+                                         int dv, int page_size, int block, int num_pages, long long num_sum_slots, void* stream) { \
+    return ptl::pool_blocks<TYPE>(summary, cache, block_table, tok_req, positions, sum_slots, tokens, bt_stride, G, d, dv,          \
+                                  page_size, block, num_pages, num_sum_slots, stream);                                             \
   }
 PTL_WINDOW_ATTENTION(_f32, float)
 PTL_WINDOW_ATTENTION(_bf16, __nv_bfloat16)

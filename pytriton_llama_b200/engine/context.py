@@ -33,13 +33,17 @@ class LayerCacheView:
     state: Optional[torch.Tensor]   # [slots, *state_shape] per-request state of this entry
     write: bool = True              # False: read what another run of a layer stored
     states: Dict[str, torch.Tensor] = field(default_factory=dict)   # named per-request states: [slots, *shape] float32
+    summary_group: Optional[GroupStepView] = None   # paging data of the entry's block means (``CacheNeed.pool_block``): the slot
+                                                    # of a token is where the mean of the block it completes goes (-1: it completes none)
+    summary: Optional[torch.Tensor] = None          # [pages, kv_heads * page_size * (head_dim + value_dim)], mean keys first
 
     def member(self, prefix: str) -> "LayerCacheView":
         """The view of one member of a mixer made of several: the states whose names start with
         ``prefix`` + ".", under their own names."""
         cut = len(prefix) + 1
         return LayerCacheView(self.group, self.kv, self.state, self.write,
-                              {k[cut:]: v for k, v in self.states.items() if k.startswith(prefix + ".")})
+                              {k[cut:]: v for k, v in self.states.items() if k.startswith(prefix + ".")},
+                              self.summary_group, self.summary)
 
 
 @dataclass
@@ -62,3 +66,5 @@ class StepContext:
     tokens: Optional[torch.Tensor] = None   # int32 [T] the step's token ids (set by the model's forward pass)
     # integer lists the operator set asked for (``ops.plan_step``): name -> ``StepWork``
     work: Dict[str, Any] = field(default_factory=dict)
+    # what a part of one layer leaves for parts of later layers of the same step (the results of all layers so far, ...)
+    scratch: Dict[str, Any] = field(default_factory=dict)

@@ -205,6 +205,8 @@ class Engine:
             if need.kind in ("full", "window", "chunk"):
                 k = need.group_key()
                 per_page[k] = per_page.get(k, 0) + need.kv_heads * (need.head_dim + need.stored_v_dim) * self.config.page_size * esize
+                if need.pool_block:      # its share of a page of block means
+                    per_page[k] += -(-need.kv_heads * (need.head_dim + need.stored_v_dim) * self.config.page_size * esize // need.pool_block)
         if not per_page:
             return 1
         bytes_per_page = sum(per_page.values())   # one page in every group
@@ -414,8 +416,10 @@ class Engine:
         def cache_view(entry: int, write: bool) -> LayerCacheView:
             g = cache.entry_group[entry]
             grp = cache.groups[g]
+            gs = cache.entry_summary_group.get(entry)
             return LayerCacheView(group=groups.get(g), kv=grp.kv.get(entry), state=grp.state.get(entry), write=write,
-                                  states=grp.states.get(entry, {}))
+                                  states=grp.states.get(entry, {}), summary_group=groups.get(gs) if gs is not None else None,
+                                  summary=cache.groups[gs].kv.get(entry) if gs is not None else None)
         return ctx, cache_view
 
     def _choose_splits(self, tokens: int, max_ctx: int) -> int:

@@ -48,7 +48,13 @@ _SIGNATURES = {
     "ptl_qk_norm_rotate_store": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _c_int, _c_f, _ptr,
                                  _ptr, _c_int, _c_ll, _ptr],
     "ptl_window_attention": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                             _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _c_f, _c_int, _ptr],
+                             _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _c_f, _c_int, _c_f, _c_int,
+                             _c_int, _ptr, _ptr, _c_int, _c_int, _ptr],
+    "ptl_head_norm_rotate_store": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _c_int, _ptr,
+                                   _ptr, _c_int, _c_ll, _ptr],
+    "ptl_pool_blocks": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _ptr],
+    "ptl_post_norm_add": [_ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _c_f, _ptr, _ptr, _c_ll, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int,
+                          _c_int, _ptr],
     "ptl_add_layernorm": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _c_int, _ptr],
     "ptl_xielu": [_ptr, _ptr, _c_ll, _c_f, _c_f, _ptr],
     "ptl_general_delta_scan": [_ptr, _ptr, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _c_f, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int,
@@ -60,7 +66,8 @@ _SIGNATURES = {
     "ptl_latent_gather": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr],
     "ptl_causal_softmax_rows": [_ptr, _c_int, _ptr, _c_ll, _c_int, _ptr, _c_int, _c_f, _c_int, _ptr],
     "ptl_head_linear": [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr],
-    "ptl_gla_scan": [_ptr, _ptr, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr],
+    "ptl_gla_scan": [_ptr, _ptr, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr, _c_f,
+                     _ptr],
     "ptl_moe_gather": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr],
     "ptl_moe_grouped": [_ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr],
     "ptl_moe_combine": [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr],
@@ -164,7 +171,7 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_prefill_attention_opts_bf16.restype = _c_int
     lib.ptl_moe_tile_rows.argtypes = []
     lib.ptl_moe_tile_rows.restype = _c_int
-    lib.ptl_moe_route.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
+    lib.ptl_moe_route.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr]
     lib.ptl_moe_route.restype = _c_int
     lib.ptl_moe_plan.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr]
     lib.ptl_moe_plan.restype = _c_int
@@ -281,6 +288,7 @@ class CudaOps:
         "add_layernorm": "norm", "xielu": "elementwise", "lowrank_tanh_linear": "recurrent", "general_delta_scan": "recurrent",
         "latent_norm_store": "rope", "rotate_head_part": "rope", "head_linear": "product",
         "latent_gather": "attention", "causal_softmax_rows": "attention",
+        "head_norm_rotate_store": "rope", "pool_blocks": "attention", "post_norm_add": "norm", "mean_of_normed": "norm",
     }
 
     def enable_timing(self) -> None:
@@ -1104,11 +1112,17 @@ class CudaOps:
     def window_attention(self, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor,
                          positions: torch.Tensor, H: int, G: int, d: int, dv: int, page_size: int, scale: float, window: int = 0,
                          keep_first: int = 0, splits: int = 1, hints=None, sink: bool = False, temp_coef: float = 0.0,
-                         temp_every: int = 1, shared_values: bool = False) -> torch.Tensor:
+                         temp_every: int = 1, shared_values: bool = False, distance_bias: float = 0.0, gate_column: int = -1,
+                         pool: int = 0, summary: Optional[torch.Tensor] = None,
+                         summary_table: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Softmax attention of every token over the keys j <= p of its request with p - j < window or j < keep_first
         (window 0: all); q is [T, >= H*d], the result [T, H*dv].  ``sink``: one more term of score 0 in the
         denominator; ``temp_coef``: scores of the query at position p times 1 + temp_coef * ln(floor((p + 1) /
-        temp_every) + 1); ``shared_values``: the cache's pages hold keys only and a key's first dv entries are its value."""
+        temp_every) + 1); ``shared_values``: the cache's pages hold keys only and a key's first dv entries are its value.
+        ``distance_bias`` = c: head h takes 2^(-c (h + 1) / H) * (p - j) off its scores; ``gate_column``: the heads are
+        multiplied by the sigmoid of q's columns from there; ``pool`` = P with ``summary`` (pages of mean keys and
+        values, laid out as the cache's) and its block table: every block of P positions that lies wholly behind the
+        window is seen as its mean."""
         self._want(q, "q")
         self._want(cache, "cache", q.dtype)
         for name, t in (("block_table", block_table), ("tok_req", tok_req), ("positions", positions)):
@@ -1117,15 +1131,25 @@ class CudaOps:
             raise KernelError("window_attention: the cache's pages do not fit the heads")
         tokens = q.shape[0]
         out = self.empty((tokens, H * dv), q.dtype)
-        options = (int(bool(shared_values)), int(bool(sink)), float(temp_coef), int(temp_every))
-        if (q.dtype == torch.bfloat16 and d == dv and d in (64, 128) and not shared_values and self._work(hints, "prefill_tiles") is not None
+        if pool and window:
+            self._want(summary, "summary", q.dtype)
+            self._want(summary_table, "summary_table", torch.int32)
+            if summary[0].numel() != cache[0].numel():
+                raise KernelError("window_attention: the pages of block means do not fit the cache's")
+            pooled = (int(pool), _p(summary), _p(summary_table), summary_table.shape[1], summary.shape[0])
+        else:
+            pooled = (0, None, None, 0, 0)
+        options = (int(bool(shared_values)), int(bool(sink)), float(temp_coef), int(temp_every), float(distance_bias),
+                   int(gate_column), *pooled)
+        plain = not (distance_bias or gate_column >= 0 or pooled[0])
+        if (plain and q.dtype == torch.bfloat16 and d == dv and d in (64, 128) and not shared_values and self._work(hints, "prefill_tiles") is not None
                 and self._work(hints, "decode_items") is not None and os.environ.get("PTL_WINDOW_TC", "1") != "0"):
             if self._window_attention_tensor_cores(out, q, cache, block_table, tok_req, positions, H, G, d, page_size, scale,
                                                    window, keep_first, hints, options):
                 return out
         longest = getattr(hints, "max_ctx_len", 0) or block_table.shape[1] * page_size
         if window:
-            longest = min(longest, window + keep_first)
+            longest = min(longest, window + keep_first + (longest // pooled[0] + 32 if pooled[0] else 0))
         splits = self._window_splits(tokens, H, longest)
         self._window_attention_simt(out, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window,
                                     keep_first, splits, None, options)
@@ -1139,7 +1163,10 @@ class CudaOps:
     def _window_attention_simt(self, out, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window,
                                keep_first, splits, rows, options=(0, 0, 0.0, 1)) -> None:
         """``rows``: None for every token row, else (int32 row indices or None for 0..n-1, n).  ``options``: (values
-        inside the keys, sink term, temperature coefficient, temperature step)."""
+        inside the keys, sink term, temperature coefficient, temperature step[, distance bias exponent, gate column,
+        block length of the means, their pages, their block table, its width, number of their pages])."""
+        if len(options) == 4:
+            options = (*options, 0.0, -1, 0, None, None, 0, 0)
         tokens = q.shape[0]
         items, n_rows = (None, tokens) if rows is None else rows
         part_acc = part_ml = None
@@ -1162,7 +1189,7 @@ class CudaOps:
             rc = self.lib.ptl_prefill_attention_opts_bf16(
                 _p(out), _p(q), _p(cache), _p(block_table), _p(tiles.tensor), tiles.items, q.shape[1], H * d, block_table.shape[1],
                 H, G, d, page_size, float(scale), int(window), int(keep_first), cache.shape[0], options[1], options[2], options[3],
-                self._stream())
+                self._stream())      # (steps with a distance bias, a gate or block means never come here)
             if rc == -2:
                 return False
             self._check(rc)
@@ -1175,20 +1202,126 @@ class CudaOps:
                                         (None if dec.in_order else dec.tensor, dec.items), options)
         return True
 
-    def gla_scan(self, proj: torch.Tensor, z: torch.Tensor, bias: torch.Tensor, inv_tau: float, state: torch.Tensor, ctx, H: int,
-                 d: int, dv: int, q_scale: float) -> torch.Tensor:
+    def gla_scan(self, proj: torch.Tensor, z: Optional[torch.Tensor], bias: Optional[torch.Tensor], inv_tau: float,
+                 state: torch.Tensor, ctx, H: int, d: int, dv: int, q_scale: float, head_decay: Optional[torch.Tensor] = None,
+                 k_scale: float = 1.0) -> torch.Tensor:
         """The recurrence of ``parts/gla.py``: proj [T, q | k | v | ...], z float32 [T, H*d] (the decay's argument before
-        its bias); state float32 [slots, H, d, dv]; returns the heads' read-outs, float32 [T, H*dv]."""
+        its bias); state float32 [slots, H, d, dv]; returns the heads' read-outs, float32 [T, H*dv].  With ``head_decay``
+        float32 [H] and no ``z`` every channel of a head decays by that fixed factor (``parts/retention.py``);
+        ``k_scale`` multiplies the keys."""
         self._want(proj, "proj")
-        for name, t in (("z", z), ("bias", bias), ("state", state)):
-            self._want(t, name, torch.float32)
-        if z.shape[1] != H * d or bias.shape[0] != H * d or tuple(state.shape[1:]) != (H, d, dv):
+        self._want(state, "state", torch.float32)
+        if z is None:
+            self._want(head_decay, "head_decay", torch.float32)
+            if head_decay.numel() != H:
+                raise KernelError("gla_scan: one decay per head")
+        else:
+            for name, t in (("z", z), ("bias", bias)):
+                self._want(t, name, torch.float32)
+            if z.shape[1] != H * d or bias.shape[0] != H * d:
+                raise KernelError("gla_scan: shapes do not fit")
+        if tuple(state.shape[1:]) != (H, d, dv):
             raise KernelError("gla_scan: shapes do not fit")
         out = self.empty((proj.shape[0], H * dv), torch.float32)
         fn = getattr(self.lib, "ptl_gla_scan" + _suffix(proj.dtype))
         self._check(fn(_p(out), _p(proj), proj.shape[1], _p(z), _p(bias), float(inv_tau), _p(state), _p(ctx.q_start), _p(ctx.positions),
-                       _p(ctx.state_slot), ctx.num_requests, H, d, dv, float(q_scale), self._stream()))
+                       _p(ctx.state_slot), ctx.num_requests, H, d, dv, float(q_scale), _p(head_decay) if z is None else None,
+                       float(k_scale), self._stream()))
         return out
+
+    # ------------------------------------------------------------------ operators of the Podizen parts
+    def head_norm_rotate_store(self, proj: torch.Tensor, H: int, G: int, d: int, dv: int, q_norm: Optional[torch.Tensor],
+                               k_norm: Optional[torch.Tensor], eps: float, positions: torch.Tensor,
+                               inv_freq: Optional[torch.Tensor], rot: int, slots: Optional[torch.Tensor],
+                               cache: Optional[torch.Tensor], page_size: int) -> None:
+        """On proj [T, q | k | v | ...] (H heads of d, G of d, G of dv; G = 0: nothing is stored), in place: every q and k
+        head divided by its own root mean square and multiplied by the weight [d] of its kind (eps > 0), entries i and
+        i + rot/2 of every head turned by position * inv_freq[i]; k and v go to the tokens' slots of a cache whose pages
+        hold keys, then values."""
+        self._want(proj, "proj")
+        self._want(positions, "positions", torch.int32)
+        for name, t in (("q norm", q_norm), ("k norm", k_norm), ("inv_freq", inv_freq)):
+            if t is not None:
+                self._want(t, name, torch.float32)
+        if eps > 0 and (q_norm.numel() != d or (G and k_norm.numel() != d)):
+            raise KernelError("head_norm_rotate_store: the norm weights have the size of a head")
+        num_slots = 0
+        if G and cache is not None:
+            self._want(cache, "cache", proj.dtype)
+            self._want(slots, "slots", torch.int32)
+            if cache[0].numel() != G * page_size * (d + dv):
+                raise KernelError("head_norm_rotate_store: the cache's pages do not fit the heads")
+            num_slots = cache.shape[0] * page_size
+        if inv_freq is not None and inv_freq.numel() < rot // 2:
+            raise KernelError("head_norm_rotate_store: fewer frequencies than pairs")
+        fn = getattr(self.lib, "ptl_head_norm_rotate_store" + _suffix(proj.dtype))
+        self._check(fn(_p(proj), proj.shape[0], proj.shape[1], H, G, d, dv, _p(q_norm), _p(k_norm), float(eps), _p(positions),
+                       _p(inv_freq), int(rot) if inv_freq is not None else 0, _p(slots) if G else None, _p(cache) if G else None,
+                       page_size, num_slots, self._stream()))
+
+    def pool_blocks(self, cache: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor, positions: torch.Tensor,
+                    summary_slots: torch.Tensor, summary: torch.Tensor, G: int, d: int, dv: int, page_size: int, block: int) -> None:
+        """For every token with a slot (>= 0) in ``summary``: the mean key and mean value of the ``block`` positions that
+        end with the token's own, read from the cache's pages, written to that slot."""
+        self._want(cache, "cache")
+        self._want(summary, "summary", cache.dtype)
+        for name, t in (("block_table", block_table), ("tok_req", tok_req), ("positions", positions), ("summary_slots", summary_slots)):
+            self._want(t, name, torch.int32)
+        if cache[0].numel() != G * page_size * (d + dv) or summary[0].numel() != cache[0].numel():
+            raise KernelError("pool_blocks: the pages do not fit the heads")
+        fn = getattr(self.lib, "ptl_pool_blocks" + _suffix(cache.dtype))
+        self._check(fn(_p(summary), _p(cache), _p(block_table), _p(tok_req), _p(positions), _p(summary_slots), positions.shape[0],
+                       block_table.shape[1], G, d, dv, page_size, int(block), cache.shape[0], summary.shape[0] * page_size,
+                       self._stream()))
+
+    def post_norm_add(self, outs, weights, post_weight: torch.Tensor, eps: float, residual: torch.Tensor, dtype=None,
+                      results: Optional[torch.Tensor] = None, index: int = 0, coeffs: Optional[torch.Tensor] = None,
+                      next_weight: Optional[torch.Tensor] = None):
+        """u = outs[0], or with ``weights`` the mean over m of rmsnorm(outs[m]) * weights[m];  X = residual + rmsnorm(u) *
+        post_weight.  With ``results`` float32 [n, T, W]: results[index] = X and the stream becomes
+        sum_{j <= index} coeffs[j] * results[j], else the stream is X.  The stream is written over ``residual``.  Returns
+        (rmsnorm(stream) * next_weight in ``dtype`` or None, residual).  One kernel."""
+        a0 = outs[0]
+        self._want(a0, "sub-layer output")
+        self._want(residual, "residual", torch.float32)
+        self._want(post_weight, "post weight", torch.float32)
+        T, W = residual.shape
+        dtype = dtype or a0.dtype
+        members = 0 if weights is None else len(outs)
+        if members > 2 or len(outs) > (members or 1):
+            raise KernelError("post_norm_add: at most two members")
+        for o in outs:
+            if tuple(o.shape) != (T, W) or o.dtype != a0.dtype or not o.is_contiguous():
+                raise KernelError("post_norm_add: the outputs do not fit the stream")
+        if a0.dtype not in (dtype, torch.float32):
+            raise KernelError("post_norm_add: outputs are of the compute type or float32")
+        stride = 0
+        if results is not None:
+            self._want(results, "results", torch.float32)
+            self._want(coeffs, "coeffs", torch.float32)
+            if tuple(results.shape[1:]) != (T, W) or not 0 <= index < results.shape[0] or coeffs.numel() <= index:
+                raise KernelError("post_norm_add: the buffer of results does not fit")
+            stride = results.stride(0)
+        y = self.empty((T, W), dtype) if next_weight is not None else None
+        fn = getattr(self.lib, "ptl_post_norm_add" + _suffix(dtype))
+        self._check(fn(_p(a0), _p(outs[1]) if members > 1 else None, _p(weights[0]) if members else None,
+                       _p(weights[1]) if members > 1 else None, members, _p(post_weight), float(eps), _p(residual), _p(results),
+                       stride, int(index), _p(coeffs), _p(next_weight), _p(y), T, W, int(a0.dtype == torch.float32 and dtype != torch.float32),
+                       self._stream()))
+        return y, residual
+
+    def mean_of_normed(self, members, eps: float, dtype) -> torch.Tensor:
+        """(1 / M) sum_m rmsnorm(x_m) * w_m over ``members`` = [(x_m [T, W], w_m float32 [W])], M <= 2."""
+        outs, weights = [x for x, _ in members], [w for _, w in members]
+        if not 1 <= len(outs) <= 2:
+            raise KernelError("mean_of_normed: one or two members")
+        T, W = outs[0].shape
+        y = self.empty((T, W), dtype)
+        fn = getattr(self.lib, "ptl_post_norm_add" + _suffix(dtype))
+        self._check(fn(_p(outs[0]), _p(outs[1]) if len(outs) > 1 else None, _p(weights[0]), _p(weights[1]) if len(outs) > 1 else None,
+                       len(outs), None, float(eps), None, None, 0, 0, None, None, _p(y), T, W,
+                       int(outs[0].dtype == torch.float32 and dtype != torch.float32), self._stream()))
+        return y
 
     # ------------------------------------------------------------------ operators of the Sogalix parts
     def add_layernorm(self, x: Optional[torch.Tensor], residual: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor,
@@ -1430,10 +1563,13 @@ class CudaOps:
     MOE_WIDE_MIN_ROWS = int(os.environ.get("PTL_MOE_WIDE_MIN", "512"))   # (token, choice) pairs from which tiles of 128 rows pay
 
     def routed_experts(self, x: torch.Tensor, logits: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top: int,
-                       scale_input: bool, shared: Optional[torch.Tensor]) -> torch.Tensor:
+                       scale_input: bool, shared: Optional[torch.Tensor], score: str = "sigmoid", groups: int = 1,
+                       keep_groups: int = 1, renormalise: bool = False) -> torch.Tensor:
         """x [T, width], router logits float32 [T, E], expert weights [E, 2*inter, width] (gate rows, then up rows) and
         [E, width, inter]: every token's ``top`` experts by sigmoid(logit), weighted by that score on the expert's input
-        (``scale_input``) or output, summed, plus ``shared`` [T, width]; float32 [T, width].  Six kernels and no word
+        (``scale_input``) or output, summed, plus ``shared`` [T, width]; float32 [T, width].  ``score`` "softmax": the
+        scores are the softmax over all experts; ``groups`` > 1: only experts of the ``keep_groups`` groups of neighbours
+        with the largest best score can be chosen; ``renormalise``: chosen scores divided by their sum.  Six kernels and no word
         back to the host: route, plan (sort by expert), gather, two grouped products, combine.  The products walk tiles
         of 32 rows of one expert; in bfloat16 steps with many tokens walk tiles of 128 rows."""
         self._want(x, "x")
@@ -1459,7 +1595,10 @@ class CudaOps:
         wide = ints[2 * n + 3 * max_tiles:2 * n + 3 * max_tiles + 3 * max_wide] if use_wide else None
         meta = ints[2 * n + 3 * max_tiles + 3 * max_wide:]
         weights = self.empty((n,), torch.float32)
-        self._check(self.lib.ptl_moe_route(_p(ids), _p(weights), _p(logits), T, E, top, stream))
+        if score not in ("sigmoid", "softmax"):
+            raise KernelError(f"routed_experts: score {score!r}")
+        self._check(self.lib.ptl_moe_route(_p(ids), _p(weights), _p(logits), T, E, top, int(score == "softmax"), int(groups),
+                                           int(keep_groups) if groups > 1 else 1, int(bool(renormalise)), stream))
         self._check(self.lib.ptl_moe_plan(_p(pos), _p(tiles), _p(meta), _p(ids), n, E, max_tiles, _p(wide), max_wide, stream))
         rows = max_tiles * tile
         sorted_x = self.empty((rows, width), x.dtype)

@@ -71,7 +71,9 @@ class CacheNeed:
     (None if none).  ``states``: further per-request states by name, float32, as (name, shape)
     pairs; a mixer made of several lists those of all its members.  ``keep_first`` (kind "window"):
     the keys of positions below it stay visible, and held, whatever the window has passed.
-    ``shared_values``: a key's first ``value_dim`` entries are its value; no values are stored."""
+    ``shared_values``: a key's first ``value_dim`` entries are its value; no values are stored.
+    ``pool_block`` = P > 0: beside its pages of keys and values the entry keeps, in pages of their own, one mean key
+    and one mean value for every complete block of P positions of a request (never given back before the request ends)."""
     kind: str = "none"
     kv_heads: int = 0
     head_dim: int = 0
@@ -82,6 +84,7 @@ class CacheNeed:
     states: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
     keep_first: int = 0
     shared_values: bool = False
+    pool_block: int = 0
 
     @property
     def v_dim(self) -> int:
@@ -94,7 +97,7 @@ class CacheNeed:
 
     def group_key(self):
         return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape, self.state_dtype,
-                self.value_dim, self.states, self.keep_first, self.shared_values)
+                self.value_dim, self.states, self.keep_first, self.shared_values, self.pool_block)
 
     def merged(self, other: "CacheNeed") -> "CacheNeed":
         """The need of a cache entry that ``self`` and ``other`` both read: everything either of them

@@ -334,7 +334,8 @@ class TorchOps:
                 vp[:, off] = proj[t, (H + G) * d:(H + G) * d + G * dv].view(G, dv)
 
     def window_attention(self, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window=0, keep_first=0,
-                         splits=1, hints=None, sink=False, temp_coef=0.0, temp_every=1, shared_values=False):
+                         splits=1, hints=None, sink=False, temp_coef=0.0, temp_every=1, shared_values=False, distance_bias=0.0,
+                         gate_column=-1, pool=0, summary=None, summary_table=None):
         T = q.shape[0]
         out = torch.zeros((T, H * dv), dtype=torch.float64)
         group = H // G
@@ -344,6 +345,13 @@ class TorchOps:
                 continue
             keys = [j for j in range(p + 1) if not window or p - j < window or j < keep_first]
             ks, vs = [], []
+            n_blocks = max(0, (p - window + 1) // pool) if pool and window else 0     # blocks that lie wholly behind the window
+            for b in range(n_blocks):
+                page = int(summary_table[r, b // page_size])
+                assert page >= 0, "attention reads a page of block means that is not held"
+                kp, vp = self._page_views(summary, page, G, page_size, d, dv)
+                ks.append(kp[:, b % page_size].double())
+                vs.append(vp[:, b % page_size].double())
             for j in keys:
                 page = int(block_table[r, j // page_size])
                 assert page >= 0, "attention reads a page that was given back"
@@ -357,8 +365,11 @@ class TorchOps:
             k, v = torch.stack(ks), torch.stack(vs)
             qt = q[t, :H * d].double().view(H, d)
             temp = 1.0 + temp_coef * math.log((p + 1) // temp_every + 1.0) if temp_coef else 1.0
+            dist = torch.tensor([0.0] * n_blocks + [float(p - j) for j in keys], dtype=torch.float64)
             for h in range(H):
                 sc = (k[:, h // group] @ qt[h]) * scale * temp
+                if distance_bias:
+                    sc = sc - 2.0 ** (-distance_bias * (h + 1) / H) * dist
                 if sink:
                     m = max(float(sc.max()), 0.0)
                     ex = torch.exp(sc - m)
@@ -366,15 +377,92 @@ class TorchOps:
                 else:
                     w = torch.softmax(sc, 0)
                 out[t, h * dv:(h + 1) * dv] = w @ v[:, h // group]
+        if gate_column >= 0:
+            out = out * torch.sigmoid(q[:, gate_column:gate_column + H * dv].double())
         return out.to(q.dtype)
 
-    def gla_scan(self, proj, z, bias, inv_tau, S_all, ctx, H, d, dv, q_scale):
+    def head_norm_rotate_store(self, proj, H, G, d, dv, q_norm, k_norm, eps, positions, inv_freq, rot, slots, cache, page_size):
+        """proj [T, q | k | v | ...] in place: every q and k head divided by its own root mean square and multiplied by
+        the weight [d] of its kind (eps > 0), entries i and i + rot/2 turned by position * inv_freq[i]; k, v to the cache."""
+        T = proj.shape[0]
+        qk = proj[:, :(H + G) * d].double().view(T, H + G, d).clone()
+        if eps > 0:
+            qk = qk / torch.sqrt((qk * qk).mean(-1, keepdim=True) + eps)
+            qk[:, :H] = qk[:, :H] * q_norm.double()
+            if G:
+                qk[:, H:] = qk[:, H:] * k_norm.double()
+        if inv_freq is not None and rot > 0:
+            half = rot // 2
+            ang = positions.double()[:, None] * inv_freq.double()[None, :half]
+            c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            a, b = qk[..., :half].clone(), qk[..., half:rot].clone()
+            qk[..., :half] = a * c - b * s
+            qk[..., half:rot] = b * c + a * s
+        proj[:, :(H + G) * d] = qk.reshape(T, -1).to(proj.dtype)
+        if G and cache is not None:
+            for t in range(T):
+                sl = int(slots[t])
+                if sl < 0:
+                    continue
+                page, off = divmod(sl, page_size)
+                kp, vp = self._page_views(cache, page, G, page_size, d, dv)
+                kp[:, off] = proj[t, H * d:(H + G) * d].view(G, d)
+                vp[:, off] = proj[t, (H + G) * d:(H + G) * d + G * dv].view(G, dv)
+
+    def pool_blocks(self, cache, block_table, tok_req, positions, summary_slots, summary, G, d, dv, page_size, block):
+        """For every token with a slot in the pages of block means: the mean key and mean value of the ``block``
+        positions that end with the token's own, read from the cache."""
+        for t in range(positions.shape[0]):
+            sl, r, p = int(summary_slots[t]), int(tok_req[t]), int(positions[t])
+            if sl < 0 or r < 0:
+                continue
+            ks, vs = [], []
+            for j in range(p - block + 1, p + 1):
+                page = int(block_table[r, j // page_size])
+                assert page >= 0, "a block's mean reads a page that was given back"
+                kp, vp = self._page_views(cache, page, G, page_size, d, dv)
+                ks.append(kp[:, j % page_size].double())
+                vs.append(vp[:, j % page_size].double())
+            kp, vp = self._page_views(summary, sl // page_size, G, page_size, d, dv)
+            kp[:, sl % page_size] = torch.stack(ks).mean(0).to(summary.dtype)
+            vp[:, sl % page_size] = torch.stack(vs).mean(0).to(summary.dtype)
+
+    def mean_of_normed(self, members, eps, dtype):
+        total = 0.0
+        for x, w in members:
+            x = x.double()
+            total = total + x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w.double()
+        return (total / len(members)).to(dtype)
+
+    def post_norm_add(self, outs, weights, post_weight, eps, residual, dtype=None, results=None, index=0, coeffs=None,
+                      next_weight=None):
+        """u = outs[0], or with ``weights`` the mean over m of rmsnorm(outs[m]) * weights[m];  X = residual + rmsnorm(u) *
+        post_weight.  With ``results`` [n, T, W]: results[index] = X and the stream becomes sum_{j <= index} coeffs[j] *
+        results[j], else the stream is X.  The stream is written over ``residual``.  Returns (rmsnorm(stream) * next_weight
+        in ``dtype`` or None, residual)."""
+        unit = lambda x: x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+        if weights is None:
+            u = outs[0].double()
+        else:
+            u = sum(unit(o.double()) * w.double() for o, w in zip(outs, weights)) / len(outs)
+        X = residual.double() + unit(u) * post_weight.double()
+        if results is not None:
+            results[index] = X.float()
+            X = sum(coeffs[j].double() * results[j].double() for j in range(index)) + coeffs[index].double() * X
+        residual.copy_(X.float())
+        y = (unit(X) * next_weight.double()).to(dtype) if next_weight is not None else None
+        return y, residual
+
+    def gla_scan(self, proj, z, bias, inv_tau, S_all, ctx, H, d, dv, q_scale, head_decay=None, k_scale=1.0):
         T = proj.shape[0]
         x = proj.double()
         q = x[:, :H * d].view(T, H, d) * q_scale
-        k = x[:, H * d:2 * H * d].view(T, H, d)
+        k = x[:, H * d:2 * H * d].view(T, H, d) * k_scale
         v = x[:, 2 * H * d:2 * H * d + H * dv].view(T, H, dv)
-        decay = torch.exp(torch.nn.functional.logsigmoid(z.double() + bias.double()) * inv_tau).view(T, H, d)
+        if head_decay is not None:          # one fixed decay per head
+            decay = head_decay.double()[None, :, None].expand(T, H, d)
+        else:
+            decay = torch.exp(torch.nn.functional.logsigmoid(z.double() + bias.double()) * inv_tau).view(T, H, d)
         o = torch.zeros((T, H, dv), dtype=torch.float64)
         for lo, hi, slot, pos0 in self._requests(ctx):
             S = S_all[slot].double() if pos0 > 0 else torch.zeros((H, d, dv), dtype=torch.float64)
@@ -388,14 +476,25 @@ class TorchOps:
         z = x.double()
         return (0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))).to(x.dtype)
 
-    def routed_experts(self, x, logits, w_gate_up, w_down, top, scale_input, shared):
+    def routed_experts(self, x, logits, w_gate_up, w_down, top, scale_input, shared, score="sigmoid", groups=1, keep_groups=1,
+                       renormalise=False):
         T = x.shape[0]
+        E = logits.shape[1]
         inter = w_gate_up.shape[1] // 2
-        score = torch.sigmoid(logits.double())
+        score = torch.softmax(logits.double(), dim=-1) if score == "softmax" else torch.sigmoid(logits.double())
         out = torch.zeros((T, w_down.shape[1]), dtype=torch.float64)
         for t in range(T):
-            for e in score[t].topk(top).indices.tolist():
-                w = score[t, e]
+            allowed = score[t].clone()
+            if groups > 1 and keep_groups < groups:
+                best = score[t].view(groups, E // groups).max(dim=1).values
+                kept = set(best.topk(keep_groups).indices.tolist())
+                for e in range(E):
+                    if e // (E // groups) not in kept:
+                        allowed[e] = -1.0
+            chosen = allowed.topk(top).indices.tolist()
+            total = sum(score[t, e] for e in chosen) + 1e-20 if renormalise else 1.0
+            for e in chosen:
+                w = score[t, e] / total
                 u = (x[t].double() * w).to(x.dtype).double() if scale_input else x[t].double()
                 gu = w_gate_up[e].double() @ u
                 g, up = gu[:inter], gu[inter:]
