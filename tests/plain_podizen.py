@@ -173,7 +173,7 @@ def moe_feed_forward(h, mlp: dict, W, p: str) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- the model
-def layer(x, L: dict, W, p: str, eps: float) -> torch.Tensor:
+def run_layer(x, L: dict, W, p: str, eps: float) -> torch.Tensor:
     h = rms_norm(x, W[p + "norm1"], eps)
     if L["type"] == "attention":
         y = gated_attention_mixer(h, L["mixer"], W, p + "mix.")
@@ -195,7 +195,7 @@ def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int], return_lay
     results = [x]                                   # the embedding output, then every layer's own result
     handed = []
     for i, L in enumerate(cfg["layers"]):
-        results.append(layer(x, L, W, f"l{i}.", eps))
+        results.append(run_layer(x, L, W, f"l{i}.", eps))
         a = W[f"l{i}.dwa"].to(F)
         x = sum(a[j] * results[j] for j in range(i + 2))
         handed.append(x)
@@ -223,3 +223,162 @@ def load_model_folder(folder, dtype=F):
         t = torch.frombuffer(bytearray(raw[8 + n + lo:8 + n + hi]), dtype=types[info["dtype"]]).reshape(info["shape"])
         W[name] = t.to(dtype) if t.dtype.is_floating_point else t
     return cfg, W
+
+
+# ----------------------------------------------------------------------------- random models for the tests
+def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
+    """Name -> shape of every tensor of a model."""
+    W = int(cfg["width"])
+    out = {"embed": (int(cfg["vocab"]), W), "final.norm": (W,)}
+
+    def softmax_member(p, m, gate):
+        H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        out.update({p + "q": (H * d, W), p + "k": (G * d, W), p + "v": (G * e, W), p + "o": (W, H * e)})
+        if gate:
+            out[p + "g"] = (H * e, W)
+        else:
+            out.update({p + "q.norm": (d,), p + "k.norm": (d,)})
+
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        out.update({p + "norm1": (W,), p + "norm1b": (W,), p + "dwa": (i + 2,)})
+        if L["type"] == "attention":
+            softmax_member(p + "mix.", m, True)
+        else:
+            softmax_member(p + "mix.left.", m["left"], False)
+            r = m["right"]
+            H, d, e = r["heads"], r["dim"], r["vdim"]
+            q = p + "mix.right."
+            out.update({q + "q": (H * d, W), q + "k": (H * d, W), q + "v": (H * e, W), q + "g": (H * e, W), q + "o": (W, H * e),
+                        p + "mix.left.out": (W,), p + "mix.right.out": (W,)})
+        mlp = L.get("mlp")
+        if mlp:
+            out.update({p + "norm2": (W,), p + "norm2b": (W,)})
+            ff = mlp["expert"]["ff"]
+            out[p + "mlp.router"] = (mlp["router"]["experts"], W)
+            for x in range(mlp["router"]["experts"]):
+                out.update({f"{p}mlp.e{x}.gate": (ff, W), f"{p}mlp.e{x}.up": (ff, W), f"{p}mlp.e{x}.down": (W, ff)})
+            if mlp.get("shared"):
+                sf = mlp["shared"]["ff"]
+                out.update({p + "mlp.shared.gate": (sf, W), p + "mlp.shared.up": (sf, W), p + "mlp.shared.down": (W, sf)})
+    return out
+
+
+def random_weights(cfg: dict, seed: int, dtype=torch.float32) -> Dict[str, torch.Tensor]:
+    """Weights drawn so that no mechanism drowns: matrices N(0, 1.5^2 / fan_in), norm weights around one, depth
+    coefficients of either sign that give every result a say, router logits that spread."""
+    gen = torch.Generator().manual_seed(seed)
+    rand = lambda *s: torch.randn(*s, generator=gen, dtype=torch.float32)
+    uni = lambda lo, hi, *s: lo + (hi - lo) * torch.rand(*s, generator=gen, dtype=torch.float32)
+    out = {}
+    for name, shape in sorted(tensor_shapes(cfg).items()):
+        last = name.split(".")[-1]
+        if name == "embed":
+            t = rand(*shape) * 0.7
+        elif last in ("norm1", "norm2", "norm1b", "norm2b", "norm", "out") or name == "final.norm":
+            t = 1 + 0.2 * rand(*shape)
+        elif last == "dwa":
+            t = uni(0.3, 0.9, *shape) * torch.where(torch.arange(shape[0]) % 3 == 1, -1.0, 1.0)
+            t[-1] = t[-1].abs() + 0.3
+        elif last == "router":
+            t = rand(*shape) * (3.0 / math.sqrt(shape[-1]))
+        elif last in ("q", "k"):
+            t = rand(*shape) * (2.5 / math.sqrt(shape[-1]))
+        else:
+            t = rand(*shape) * (1.5 / math.sqrt(shape[-1]))
+        out[name] = t.to(dtype)
+    return out
+
+
+def write_model(folder, cfg: dict, seed: int, dtype=torch.float32, weights=None):
+    """A model folder (config.json, model.safetensors); returns the weights as stored."""
+    import json
+    from pathlib import Path
+    from pytriton_llama_b200.weights import write_file      # only the file format comes from the package
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    W = weights if weights is not None else random_weights(cfg, seed, dtype)
+    (folder / "config.json").write_text(json.dumps(cfg))
+    write_file(folder / "model.safetensors", W)
+    return W
+
+
+def rotation(dims, base):
+    return {"dims": dims, "base": base}
+
+
+def gated_attention(heads, kv_heads, dim, vdim, scale, size=0):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if size:
+        m["mask"] = {"size": size}
+    return m
+
+
+def pooled_attention(heads, kv_heads, dim, vdim, scale, size=0, pool=0, rot=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if size:
+        m["mask"] = {"size": size, **({"pool": pool} if pool else {})}
+    if rot:
+        m["rot"] = rot
+    return m
+
+
+def retention(heads, dim, vdim, decay, rot=None):
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)}
+    if rot:
+        m["rot"] = rot
+    return m
+
+
+def parallel(left, right):
+    return {"left": left, "right": right}
+
+
+def moe(ff, experts, top, groups=0, keep=0, shared=0):
+    router = {"experts": experts, "top": top}
+    if groups:
+        router["groups"] = {"count": groups, "keep": keep}
+    m = {"kind": "moe", "expert": {"ff": ff}, "router": router}
+    if shared:
+        m["shared"] = {"ff": shared}
+    return m
+
+
+def layer(kind, mixer, mlp):
+    return {"type": kind, "mixer": mixer, "mlp": mlp}
+
+
+def config(vocab, width, layers, eps=1e-5):
+    return {"architecture": "Podizen", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+
+
+# A parallel layer first; windows and pooled blocks that straddle pages of 4, 8 and 16; value heads larger and smaller
+# than key heads; half a head rotated on the left, a whole head on the right; a layer without a feed-forward; groups
+# of three experts of which two are kept; a router without groups.
+TINY_A = config(97, 48, [
+    layer("parallel", parallel(pooled_attention(4, 2, 16, 24, 0.3, size=11, pool=5, rot=rotation(8, 1000.0)),
+                               retention(3, 8, 12, (0.9, 0.97, 0.995), rot=rotation(8, 50.0))), moe(24, 6, 2, groups=2, keep=1, shared=16)),
+    layer("attention", gated_attention(4, 1, 16, 8, 0.25, size=9), moe(16, 4, 3)),
+    layer("parallel", parallel(pooled_attention(2, 2, 24, 16, 0.2, size=6, pool=7, rot=rotation(24, 300.0)),
+                               retention(1, 20, 40, (0.98,), rot=rotation(4, 10.0))), None),
+    layer("attention", gated_attention(6, 3, 8, 8, 0.4, size=17), moe(12, 9, 3, groups=3, keep=2)),
+])
+# An attention layer first; as many kv heads as heads; every group kept and every expert chosen; a window of one block;
+# blocks of one position; a retention that forgets at once and one that never does; no rotation on the right.
+TINY_B = config(70, 64, [
+    layer("attention", gated_attention(6, 6, 16, 16, 0.35, size=7), moe(24, 3, 3, groups=3, keep=3, shared=24)),
+    layer("parallel", parallel(pooled_attention(3, 1, 16, 32, 0.3, size=4, pool=4, rot=rotation(16, 50.0)),
+                               retention(2, 32, 8, (0.0, 1.0))), moe(16, 8, 2, groups=4, keep=2)),
+    layer("parallel", parallel(pooled_attention(2, 1, 32, 8, 0.2, size=9, pool=1),
+                               retention(2, 12, 20, (0.5, 0.999), rot=rotation(12, 1.0e6))), None),
+], eps=3e-4)
+# A window without pooled blocks, an attention that sees everything, one expert of one, a width that is no multiple of
+# eight.
+TINY_C = config(50, 36, [
+    layer("parallel", parallel(pooled_attention(3, 1, 16, 32, 0.3, size=8, rot=rotation(16, 50.0)),
+                               retention(2, 8, 8, (0.9, 0.8), rot=rotation(8, 7.0))), moe(16, 1, 1, shared=8)),
+    layer("attention", gated_attention(3, 1, 16, 32, 0.3), moe(8, 6, 1, groups=6, keep=1)),
+    layer("parallel", parallel(pooled_attention(1, 1, 8, 8, 0.5, rot=rotation(2, 3.0)),
+                               retention(1, 8, 16, (0.95,))), None),
+])
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
