@@ -266,7 +266,10 @@ def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
 
 def random_weights(cfg: dict, seed: int, dtype=torch.float32) -> Dict[str, torch.Tensor]:
     """Weights drawn so that no mechanism drowns: matrices N(0, 1.5^2 / fan_in), norm weights around one, depth
-    coefficients of either sign that give every result a say, router logits that spread."""
+    coefficients of either sign that give every result a say, router logits that spread.  In 16 bits scores are
+    smaller and the depth coefficients positive: a score s carries a rounding error of about |s| * 2^-8, and a
+    difference of two results of similar size multiplies every rounding error before it."""
+    gentle = dtype != torch.float32
     gen = torch.Generator().manual_seed(seed)
     rand = lambda *s: torch.randn(*s, generator=gen, dtype=torch.float32)
     uni = lambda lo, hi, *s: lo + (hi - lo) * torch.rand(*s, generator=gen, dtype=torch.float32)
@@ -278,12 +281,14 @@ def random_weights(cfg: dict, seed: int, dtype=torch.float32) -> Dict[str, torch
         elif last in ("norm1", "norm2", "norm1b", "norm2b", "norm", "out") or name == "final.norm":
             t = 1 + 0.2 * rand(*shape)
         elif last == "dwa":
-            t = uni(0.3, 0.9, *shape) * torch.where(torch.arange(shape[0]) % 3 == 1, -1.0, 1.0)
+            t = uni(0.3, 0.9, *shape) * torch.where((torch.arange(shape[0]) % 3 == 1) & (not gentle), -1.0, 1.0)
             t[-1] = t[-1].abs() + 0.3
+            if gentle:
+                t = t / t.sum()
         elif last == "router":
             t = rand(*shape) * (3.0 / math.sqrt(shape[-1]))
         elif last in ("q", "k"):
-            t = rand(*shape) * (2.5 / math.sqrt(shape[-1]))
+            t = rand(*shape) * ((1.2 if gentle else 2.5) / math.sqrt(shape[-1]))
         else:
             t = rand(*shape) * (1.5 / math.sqrt(shape[-1]))
         out[name] = t.to(dtype)
