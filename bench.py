@@ -4,6 +4,7 @@
     python bench.py --family tibepel      # another workload: the Tibepel decoder beside a Llama of equal size
     python bench.py --family lilenex      # likewise the Lilenex decoder
     python bench.py --family sogalix      # the Sogalix decoder beside a Lilenex and a Llama of equal size
+    python bench.py --family podizen      # the Podizen decoder beside a Lilenex and a Llama of equal size
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and context 4096, timed on
 the device with CUDA events around exactly K decode steps (a step = the engine's step function for
@@ -218,12 +219,33 @@ def _sogalix(width, layers, ff, vocab):
     return {"architecture": "Sogalix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": out}
 
 
-FAMILIES = {"tibepel": (_tibepel, ["llama"]), "lilenex": (_lilenex, ["llama"]), "sogalix": (_sogalix, ["lilenex", "llama"])}
+def _podizen(width, layers, ff, vocab):
+    """A Podizen of sizes that resemble a real model's layers.  Layers alternate between gated attention with a distance
+    bias (heads of 128, 4 query heads per kv head, a window of 1,024 positions) and the mean of a pooled-window attention
+    (heads of 128, 4 query heads per kv head, half of every head rotated, a window of 512 positions behind which blocks
+    of 16 positions are seen as their means) and a retention (heads of 128 x 128, half of every head rotated).  Every
+    layer's feed-forward has 16 experts of ff/4 in 4 groups of which 2 are kept, two experts per token, beside a shared
+    one of ff/2 (as many weights at work per token as a dense layer of ff has)."""
+    heads = width // 128
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024}}
+    left = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "mask": {"size": 512, "pool": 16}, "rot": {"dims": 64, "base": 1000000.0}}
+    right = {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - h % 8) for h in range(heads)],
+             "rot": {"dims": 64, "base": 10000.0}}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": ff // 2}}
+    return {"architecture": "Podizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention", "mixer": att, "mlp": moe} if i % 2 == 0 else
+                       {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": moe} for i in range(layers)]}
+
+
+FAMILIES = {"tibepel": (_tibepel, ["llama"]), "lilenex": (_lilenex, ["llama"]), "sogalix": (_sogalix, ["lilenex", "llama"]),
+            "podizen": (_podizen, ["lilenex", "llama"])}
 
 
 def family_bench(args) -> int:
-    """``--family tibepel``, ``lilenex`` or ``sogalix``: prefill (one step of 2,048 prompt tokens, as one prompt and as 8 prompts of 256) and decode
-    (8 requests at 1,024 tokens, a step with its sampling kernel) of that decoder and of a Llama decoder (for Sogalix also a Lilenex decoder) of the
+    """``--family tibepel``, ``lilenex``, ``sogalix`` or ``podizen``: prefill (one step of 2,048 prompt tokens, as one prompt and as 8 prompts of 256) and decode
+    (8 requests at 1,024 tokens, a step with its sampling kernel) of that decoder and of a Llama decoder (for Sogalix and Podizen also a Lilenex decoder) of the
     same width, depth, feed-forward size and vocabulary, on random weights, timed with CUDA events after warm-up; then one timed step of each kind with
     every operator bracketed by events, for the milliseconds by class of kernels.  One JSON line."""
     import torch
@@ -359,7 +381,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=None, help="decode batch (default: 8; 32 for 3b; 64 for 8b)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--points", default=None, help="extra decode batch sizes, comma separated ('' for none)")
-    ap.add_argument("--family", default=None, choices=["tibepel", "lilenex", "sogalix"],
+    ap.add_argument("--family", default=None, choices=["tibepel", "lilenex", "sogalix", "podizen"],
                     help="another workload: this decoder beside a Llama of equal size, prefill and decode (own JSON line)")
     ap.add_argument("--family-sizes", default=None, help="with --family: WIDTHxLAYERSxFF[,...] (default 1024x8x4096,2048x8x8192)")
     ap.add_argument("--no-e2e", action="store_true")

@@ -8,6 +8,12 @@
 // alike.  Scores, running max and sum, and the accumulator are float32; P is rounded to bfloat16
 // for the second product, as lite_llama's kernel does (lite_llama/kernels/flashattentionv2.py:55).
 //
+// Options (`PrefillExtras`): `bias_exp` = c > 0 takes 2^(-c (h + 1) / heads) * (position of the query - position of the
+// key) off the scores of head h; `gate_col` >= 0 multiplies the result of head h by the sigmoid of the D entries at
+// column gate_col + h * D of the token's q row; `pool` = P > 0 (with a window) puts key tiles of block means in front:
+// entry b of `summary` (pages laid out as the cache's, with a block table of their own) is the mean key and mean
+// value of positions bP .. bP + P - 1, seen by the query at position p if bP + P - 1 <= p - window.
+//
 // tiles[i] = {request row, first token index, rows (0..128; 0: nothing to do), position of the first token}.
 #include "mma_utils.cuh"
 
@@ -26,6 +32,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+struct PrefillExtras {
+  float bias_exp;
+  int gate_col, pool;
+  const __nv_bfloat16* summary;
+  const int* sum_bt;
+  int sum_bt_stride, sum_pages;
+};
+
 // MT = 16-row tiles per warp: 2 for head size 64 (4 warps), 1 for 128 (8 warps).
 template <int D, int MT> struct PrefillCfg {
   static constexpr int kWarps = kPfRows / (16 * MT);
@@ -43,7 +57,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
                          const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table,
                          const int* __restrict__ tiles, int q_stride, int out_stride, int bt_stride, int nq,
                          int nkv, int page_size, float scale_log2, int window, int num_pages, int page_shift, int keep,
-                         int sink, float temp_coef, int temp_every) {
+                         int sink, float temp_coef, int temp_every, const PrefillExtras ex) {
   using Cfg = PrefillCfg<D, MT>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_pages[kPfStagedPages];
@@ -60,7 +74,9 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const int k_end = pos0 + rows;                 // one past the last key any row of the tile sees
   // positions below `keep` stay visible when the window has passed them: those before the first window of the
   // tile come first, in key tiles of their own (no key is met twice), then the keys from k_lo on
-  const int keep_lim = min(keep, k_lo);
+  // (block means take the place of kept positions: `keep_lim` is then the number of blocks that the tile's last row sees)
+  const int pool = window > 0 ? ex.pool : 0;
+  const int keep_lim = pool > 0 ? (k_end - window > 0 ? (k_end - window) / pool : 0) : min(keep, k_lo);
   const int n_keep_tiles = (keep_lim + kPfKeys - 1) / kPfKeys;
   const int ntiles = n_keep_tiles + (k_end - k_lo + kPfKeys - 1) / kPfKeys;
   const int* bt_global = block_table + (size_t)req * bt_stride;
@@ -69,13 +85,14 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const uint32_t kv_smem = q_smem + Cfg::kQBytes;
 
   // block-table entries of the key range in shared memory (when they fit)
-  const int first_block = n_keep_tiles ? 0 : k_lo / page_size;
+  const int first_block = (n_keep_tiles && !pool) ? 0 : k_lo / page_size;
   const int n_blocks = (k_end - 1) / page_size - first_block + 1;
   const bool staged = n_blocks <= kPfStagedPages;
   if (staged) {
     for (int i = tid; i < n_blocks; i += Cfg::kThreads) s_pages[i] = bt_global[first_block + i];
   }
   const int* bt = staged ? s_pages - first_block : bt_global;
+  const int* sbt = pool ? ex.sum_bt + (size_t)req * ex.sum_bt_stride : nullptr;
 
   constexpr int kRowsPerPass = Cfg::kThreads / Cfg::kChunks;
   constexpr int kPasses = kPfKeys / kRowsPerPass;
@@ -92,16 +109,18 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
       const int row = my_row + i * kRowsPerPass;
       const int key = k0 + row;
       bool valid = key < k_limit;
+      const bool means = pool && tile < n_keep_tiles;
+      const int* table = means ? sbt : bt;
       int page, off;
       if (fast_pages) {
-        page = valid ? bt[key >> page_shift] : 0;
+        page = valid ? table[key >> page_shift] : 0;
         off = key & (page_size - 1);
       } else {
-        page = valid ? bt[key / page_size] : 0;
+        page = valid ? table[key / page_size] : 0;
         off = key % page_size;
       }
-      if (page < 0 || page >= num_pages) { valid = false; page = 0; }
-      const __nv_bfloat16* src = cache + ((size_t)page * 2) * plane + (size_t)off * D + my_const;
+      if (page < 0 || page >= (means ? ex.sum_pages : num_pages)) { valid = false; page = 0; }
+      const __nv_bfloat16* src = (means ? ex.summary : cache) + ((size_t)page * 2) * plane + (size_t)off * D + my_const;
       const uint32_t dst = tile_offset<D>(row, my_ch);
       cp_async_16(kbase + dst, src, valid);
       cp_async_16(vbase + dst, src + plane, valid);
@@ -140,6 +159,8 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const int warp_qmin = pos0 + wrow0, warp_qmax = pos0 + wrow0 + 16 * MT - 1;
   float m_run[MT][2], l_run[MT][2];
   float row_scale[MT][2];                          // the scores' factor of a row: the scale, times the query temperature of its position
+  int row_blocks[MT][2];                           // how many block means a row sees
+  const float slope2 = ex.bias_exp > 0.f ? exp2f(-ex.bias_exp * (float)(h + 1) / (float)nq) * 1.4426950408889634f : 0.f;
   float o[MT][D / 8][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
@@ -147,6 +168,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
     for (int hh = 0; hh < 2; ++hh) {
       const int qp = pos0 + wrow0 + mt * 16 + g + hh * 8;
       row_scale[mt][hh] = temp_coef != 0.f ? scale_log2 * fmaf(temp_coef, logf((float)((qp + 1) / temp_every) + 1.0f), 1.0f) : scale_log2;
+      row_blocks[mt][hh] = (pool > 0 && qp - window + 1 > 0) ? (qp - window + 1) / pool : 0;
     }
     m_run[mt][0] = m_run[mt][1] = -INFINITY;
     l_run[mt][0] = l_run[mt][1] = 0.f;
@@ -164,7 +186,9 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
     }
     const bool keep_tile = tile < n_keep_tiles;
     const int key_first = keep_tile ? tile * kPfKeys : k_lo + (tile - n_keep_tiles) * kPfKeys;
-    if (key_first > warp_qmax) continue;                       // wholly above this warp's diagonal
+    if (keep_tile && pool) {
+      if (warp_qmax - window + 1 <= 0 || key_first >= (warp_qmax - window + 1) / pool) continue;   // no row of this warp sees a block of the tile
+    } else if (key_first > warp_qmax) continue;                // wholly above this warp's diagonal
     if (!keep_tile && window > 0 && key_first >= keep && key_first + kPfKeys - 1 < warp_qmin - window + 1) continue;   // wholly before its window
     const int stage = tile % Cfg::kStages;
     const uint32_t kbase = kv_smem + stage * 2 * Cfg::kTileBytes;
@@ -190,7 +214,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
         }
       }
     }
-    const bool need_mask = keep_tile ? (key_first + kPfKeys > keep_lim)
+    const bool need_mask = keep_tile ? (key_first + kPfKeys > (pool ? (warp_qmin - window + 1 > 0 ? (warp_qmin - window + 1) / pool : 0) : keep_lim))
                                      : ((key_first + kPfKeys - 1 > warp_qmin) || (window > 0 && key_first < warp_qmax - window + 1));
     uint32_t pa[MT][kPfKeys / 16][4];
 #pragma unroll
@@ -204,7 +228,12 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
           if (need_mask) {
             const int key = key_first + nt * 8 + 2 * c + (e & 1);
             const int qp = qpos0 + (e >> 1) * 8;
-            if (keep_tile ? key >= keep_lim : (key > qp || (window > 0 && key < qp - window + 1 && key >= keep))) v = -INFINITY;
+            if (keep_tile ? key >= (pool ? row_blocks[mt][e >> 1] : keep_lim)
+                          : (key > qp || (window > 0 && key < qp - window + 1 && key >= keep))) v = -INFINITY;
+          }
+          if (slope2 != 0.f && !(keep_tile && pool)) {
+            const int key = key_first + nt * 8 + 2 * c + (e & 1);
+            v = fmaf(-slope2, (float)(qpos0 + (e >> 1) * 8 - key), v);
           }
           s[mt][nt][e] = v;
         }
@@ -267,9 +296,16 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
       }
       const float inv = l_run[mt][hh] > 0.f ? 1.0f / l_run[mt][hh] : 0.f;
       __nv_bfloat16* dst = out + (size_t)(tok0 + row) * out_stride + (size_t)h * D + 2 * c;
+      const __nv_bfloat16* gate = ex.gate_col >= 0 ? q + (size_t)(tok0 + row) * q_stride + ex.gate_col + (size_t)h * D + 2 * c : nullptr;
 #pragma unroll
       for (int i = 0; i < D / 8; ++i) {
-        *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[mt][i][2 * hh] * inv, o[mt][i][2 * hh + 1] * inv);
+        float r0 = o[mt][i][2 * hh] * inv, r1 = o[mt][i][2 * hh + 1] * inv;
+        if (gate) {
+          const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + i * 8));
+          r0 *= 1.0f / (1.0f + expf(-gv.x));
+          r1 *= 1.0f / (1.0f + expf(-gv.y));
+        }
+        *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(r0, r1);
       }
     }
 }
@@ -277,7 +313,8 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
 template <int D, int MT>
 int launch_prefill(void* out, const void* q, const void* cache, const int* block_table, const int* tiles, int n_tiles,
                    int q_stride, int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale,
-                   int window, int num_pages, void* stream, int keep = 0, int sink = 0, float temp_coef = 0.f, int temp_every = 1) {
+                   int window, int num_pages, void* stream, int keep = 0, int sink = 0, float temp_coef = 0.f, int temp_every = 1,
+                   PrefillExtras ex = {0.f, -1, 0, nullptr, nullptr, 0, 0}) {
   using Cfg = PrefillCfg<D, MT>;
   static SmemRaised raised = {};
   if (int rc = raise_shared_memory("prefill_attention", prefill_attention_kernel<D, MT>, Cfg::kSmem, raised)) return rc;
@@ -288,7 +325,7 @@ int launch_prefill(void* out, const void* q, const void* cache, const int* block
   return launch_kernel("prefill_attention", prefill_attention_kernel<D, MT>, grid, dim3(Cfg::kThreads), Cfg::kSmem,
                        as_stream(stream), (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache,
                        block_table, tiles, q_stride, out_stride, bt_stride, nq, nkv, page_size,
-                       scale * 1.4426950408889634f, window, num_pages, page_shift, keep, sink, temp_coef, temp_every);
+                       scale * 1.4426950408889634f, window, num_pages, page_shift, keep, sink, temp_coef, temp_every, ex);
 }
 
 }  // namespace ptl
@@ -338,8 +375,14 @@ PTL_EXPORT int ptl_prefill_attention_keep_bf16(void* out, const void* q, const v
 PTL_EXPORT int ptl_prefill_attention_opts_bf16(void* out, const void* q, const void* cache, const int* block_table,
                                                const int* tiles, int n_tiles, int q_stride, int out_stride, int bt_stride,
                                                int nq, int nkv, int d, int page_size, float scale, int window, int keep,
-                                               int num_pages, int sink, float temp_coef, int temp_every, void* stream) {
+                                               int num_pages, int sink, float temp_coef, int temp_every, float bias_exp,
+                                               int gate_col, int pool, const void* summary, const int* sum_bt, int sum_bt_stride,
+                                               int sum_pages, void* stream) {
   using namespace ptl;
+  PTL_REQUIRE(pool == 0 || (summary && sum_bt && sum_pages > 0 && window > 0 && keep == 0 && !sink && aligned16(summary)),
+              "prefill_attention: means of blocks need their pages and a window, and go with no kept positions or sink");
+  PTL_REQUIRE(bias_exp >= 0.f && (gate_col < 0 || (gate_col + nq * d <= q_stride && gate_col % 2 == 0)), "prefill_attention: bad bias or gate column");
+  const PrefillExtras ex = {bias_exp, gate_col, window > 0 ? pool : 0, (const __nv_bfloat16*)summary, sum_bt, sum_bt_stride, sum_pages};
   PTL_REQUIRE(n_tiles >= 0 && nq > 0 && nkv > 0 && page_size > 0 && num_pages > 0 && keep >= 0 && temp_every >= 1,
               "prefill_attention: bad sizes");
   PTL_REQUIRE(nq % nkv == 0, "prefill_attention: %d query heads are no multiple of %d kv heads", nq, nkv);
@@ -350,7 +393,7 @@ PTL_EXPORT int ptl_prefill_attention_opts_bf16(void* out, const void* q, const v
   if (window == 0) keep = 0;
   if (d == 64)
     return launch_prefill<64, PTL_PF_MT>(out, q, cache, block_table, tiles, n_tiles, q_stride, out_stride, bt_stride, nq, nkv,
-                                         page_size, scale, window, num_pages, stream, keep, sink, temp_coef, temp_every);
+                                         page_size, scale, window, num_pages, stream, keep, sink, temp_coef, temp_every, ex);
   return launch_prefill<128, 1>(out, q, cache, block_table, tiles, n_tiles, q_stride, out_stride, bt_stride, nq, nkv,
-                                page_size, scale, window, num_pages, stream, keep, sink, temp_coef, temp_every);
+                                page_size, scale, window, num_pages, stream, keep, sink, temp_coef, temp_every, ex);
 }

@@ -83,9 +83,21 @@ post_norm_add_kernel(const A* __restrict__ a0, const A* __restrict__ a1, const f
         *reinterpret_cast<float4*>(mine + i) = x;
         const float c = coeffs[index];
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int j = 0; j < index; ++j) {
+        const float* base = results + row + i;
+        int j = 0;
+        for (; j + 4 <= index; j += 4) {      // four earlier results requested together, added in ascending order
+          float4 h[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) h[u] = *reinterpret_cast<const float4*>(base + (size_t)(j + u) * result_stride);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float cj = coeffs[j + u];
+            s.x = fmaf(cj, h[u].x, s.x); s.y = fmaf(cj, h[u].y, s.y); s.z = fmaf(cj, h[u].z, s.z); s.w = fmaf(cj, h[u].w, s.w);
+          }
+        }
+        for (; j < index; ++j) {
           const float cj = coeffs[j];
-          const float4 h = *reinterpret_cast<const float4*>(results + (size_t)j * result_stride + row + i);
+          const float4 h = *reinterpret_cast<const float4*>(base + (size_t)j * result_stride);
           s.x = fmaf(cj, h.x, s.x); s.y = fmaf(cj, h.y, s.y); s.z = fmaf(cj, h.z, s.z); s.w = fmaf(cj, h.w, s.w);
         }
         x = make_float4(fmaf(c, x.x, s.x), fmaf(c, x.y, s.y), fmaf(c, x.z, s.z), fmaf(c, x.w, s.w));

@@ -167,7 +167,8 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_softcap.argtypes = [_ptr, _c_ll, _c_f, _ptr]
     lib.ptl_softcap.restype = _c_int
     lib.ptl_prefill_attention_opts_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                                    _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _ptr]
+                                                    _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_f, _c_int,
+                                                    _c_int, _ptr, _ptr, _c_int, _c_int, _ptr]
     lib.ptl_prefill_attention_opts_bf16.restype = _c_int
     lib.ptl_moe_tile_rows.argtypes = []
     lib.ptl_moe_tile_rows.restype = _c_int
@@ -1141,8 +1142,7 @@ class CudaOps:
             pooled = (0, None, None, 0, 0)
         options = (int(bool(shared_values)), int(bool(sink)), float(temp_coef), int(temp_every), float(distance_bias),
                    int(gate_column), *pooled)
-        plain = not (distance_bias or gate_column >= 0 or pooled[0])
-        if (plain and q.dtype == torch.bfloat16 and d == dv and d in (64, 128) and not shared_values and self._work(hints, "prefill_tiles") is not None
+        if (q.dtype == torch.bfloat16 and d == dv and d in (64, 128) and not shared_values and self._work(hints, "prefill_tiles") is not None
                 and self._work(hints, "decode_items") is not None and os.environ.get("PTL_WINDOW_TC", "1") != "0"):
             if self._window_attention_tensor_cores(out, q, cache, block_table, tok_req, positions, H, G, d, page_size, scale,
                                                    window, keep_first, hints, options):
@@ -1180,7 +1180,7 @@ class CudaOps:
                     kernels=2 if splits > 1 else 1)
 
     def _window_attention_tensor_cores(self, out, q, cache, block_table, tok_req, positions, H, G, d, page_size, scale, window,
-                                       keep_first, hints, options=(0, 0, 0.0, 1)) -> bool:
+                                       keep_first, hints, options=(0, 0, 0.0, 1, 0.0, -1, 0, None, None, 0, 0)) -> bool:
         """bfloat16, key and value heads of 64 or 128: the portions of a step on the tensor cores (the warp-level prompt
         kernel, which walks the kept first keys as key tiles of their own before the window's), its single tokens on
         the CUDA-core kernel with their key lists split; both write their rows of ``out``."""
@@ -1188,15 +1188,14 @@ class CudaOps:
         if tiles.items:
             rc = self.lib.ptl_prefill_attention_opts_bf16(
                 _p(out), _p(q), _p(cache), _p(block_table), _p(tiles.tensor), tiles.items, q.shape[1], H * d, block_table.shape[1],
-                H, G, d, page_size, float(scale), int(window), int(keep_first), cache.shape[0], options[1], options[2], options[3],
-                self._stream())      # (steps with a distance bias, a gate or block means never come here)
+                H, G, d, page_size, float(scale), int(window), int(keep_first), cache.shape[0], *options[1:], self._stream())
             if rc == -2:
                 return False
             self._check(rc)
         if dec.items:
             longest = getattr(hints, "max_ctx_len", 0) or block_table.shape[1] * page_size
             if window:
-                longest = min(longest, window + keep_first)
+                longest = min(longest, window + keep_first + (longest // options[6] + 32 if len(options) > 6 and options[6] else 0))
             self._window_attention_simt(out, q, cache, block_table, tok_req, positions, H, G, d, d, page_size, scale, window,
                                         keep_first, self._window_splits(dec.items, H, longest),
                                         (None if dec.in_order else dec.tensor, dec.items), options)
