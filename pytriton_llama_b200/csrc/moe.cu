@@ -40,10 +40,12 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
   const int t = blockIdx.x * (blockDim.x >> 5) + warp;
   if (t >= tokens) return;
   constexpr int kPerLane = kMoeMaxExperts / 32;
+  // (every walk over a lane's experts stops after the last turn that holds one: with few experts that is the first)
   float sc[kPerLane];
   float zmax = -INFINITY;
 #pragma unroll
   for (int i = 0; i < kPerLane; ++i) {
+    if (32 * i >= E) break;
     const int e = lane + 32 * i;
     float v = -INFINITY;
     if (e < E) {
@@ -59,6 +61,7 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
+      if (32 * i >= E) break;
       if (lane + 32 * i < E) {
         sc[i] = sc[i] > -INFINITY ? expf(sc[i] - zmax) : 0.f;
         sum += sc[i];
@@ -67,8 +70,10 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
     sum = warp_sum(sum);
     const float inv = sum > 0.f ? 1.0f / sum : 0.f;
 #pragma unroll
-    for (int i = 0; i < kPerLane; ++i)
+    for (int i = 0; i < kPerLane; ++i) {
+      if (32 * i >= E) break;
       if (lane + 32 * i < E) sc[i] *= inv;
+    }
   }
   if (groups > 1 && keep < groups) {
     const int per = E / groups;
@@ -78,6 +83,7 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
     // an expert's group is e / per; lanes hold experts 32 apart, so the groups' maxima are taken through shared memory
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
+      if (32 * i >= E) break;
       const int e = lane + 32 * i;
       if (e < E) atomicMax(reinterpret_cast<int*>(&best_of[e / per]), __float_as_int(fmaxf(sc[i], 0.f)));   // scores are >= 0: their bit patterns order as they do
     }
@@ -85,6 +91,7 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
     // a group is kept if fewer than `keep` groups beat it (a larger score, or the same score and a lower number)
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
+      if (32 * i >= E) break;
       const int e = lane + 32 * i;
       if (e < E) {
         const int mine = e / per;
@@ -95,11 +102,13 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
       }
     }
   }
+  float total = 0.f, held = 0.f;           // lane k holds the k-th chosen score (the first 32 of them)
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
+      if (32 * i >= E) break;
       const int e = lane + 32 * i;
       if (e < E && sc[i] > best) { best = sc[i]; best_e = e; }     // ascending e: the lower index stays on a tie
     }
@@ -110,17 +119,23 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
       if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
     }
     if (best_e >= E) { best_e = k % E; best = 0.f; }            // nothing finite left: a valid expert with weight 0
-    if (lane == 0) { ids[(size_t)t * top + k] = best_e; weights[(size_t)t * top + k] = best; }
+    total += best;                                               // in the order they were chosen, the same in every lane
+    if (k == lane) held = best;
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = best_e;
+      if (k >= 32) weights[(size_t)t * top + k] = best;
+    }
 #pragma unroll
-    for (int i = 0; i < kPerLane; ++i)
+    for (int i = 0; i < kPerLane; ++i) {
+      if (32 * i >= E) break;
       if (lane + 32 * i == best_e) sc[i] = -INFINITY;
+    }
   }
-  if (renorm) {
-    __syncwarp();                          // lane 0's weights, read back by all
-    float sum = 0.f;
-    for (int k = 0; k < top; ++k) sum += weights[(size_t)t * top + k];       // in the order they were chosen, the same in every lane
-    const float inv = 1.0f / (sum + 1e-20f);
-    for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= inv;
+  const float inv = renorm ? 1.0f / (total + 1e-20f) : 1.0f;
+  if (lane < top) weights[(size_t)t * top + lane] = held * inv;
+  if (renorm && top > 32) {
+    __syncwarp();                          // lane 0's weights beyond the 32nd, read back by the others
+    for (int k = 32 + lane; k < top; k += 32) weights[(size_t)t * top + k] *= inv;
   }
 }
 

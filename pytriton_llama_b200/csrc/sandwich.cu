@@ -10,6 +10,10 @@
 //   residual <- s                                            (the stream, in place)
 //   next given:       y = s * rsqrt(mean(s^2) + eps) * next  (element type T)
 //
+// Rows of up to 4,096 entries in whole packets take the fast form: a thread holds its share of the row (up to 16
+// entries) in registers, requests everything it reads from memory -- the sub-layer outputs, the residual, the earlier
+// results -- before the first sum over the block, and only then waits; the general form walks the row once per step.
+//
 // A is the element type of the sub-layer outputs (the compute type, or float32 from a routed feed-forward).
 // The row is held in shared memory between the walks; with rows of whole 16-byte packets every walk moves
 // packets.  Sums run over a thread's elements in ascending order and over the threads in a fixed tree, so a
@@ -135,6 +139,134 @@ post_norm_add_kernel(const A* __restrict__ a0, const A* __restrict__ a1, const f
   }
 }
 
+template <typename A> __device__ __forceinline__ float4 sw_load4(const A* p);
+template <> __device__ __forceinline__ float4 sw_load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 sw_load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T> __device__ __forceinline__ void sw_store4(T* p, float4 v);
+template <> __device__ __forceinline__ void sw_store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void sw_store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&a);
+  raw.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+__device__ __forceinline__ float sw_dot4(float4 v) { return fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w))); }
+
+// NP packets of four entries per thread: rows of up to 1,024 * NP entries.
+template <typename T, typename A, int NP>
+__global__ void __launch_bounds__(256)
+post_norm_add_fast_kernel(const A* __restrict__ a0, const A* __restrict__ a1, const float* __restrict__ w0,
+                          const float* __restrict__ w1, int members, const float* __restrict__ post, float eps,
+                          float* __restrict__ residual, float* __restrict__ results, long long result_stride, int index,
+                          const float* __restrict__ coeffs, const float* __restrict__ next, T* __restrict__ y, int width) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t row = (size_t)blockIdx.x * width;
+  const float inv_w = 1.0f / (float)width;
+  float4 u[NP], v[NP], r[NP], s[NP];
+  // everything this row reads from memory is requested here
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    const int i = (p * 256 + threadIdx.x) * 4;
+    u[p] = v[p] = r[p] = s[p] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < width) {
+      u[p] = sw_load4<A>(a0 + row + i);
+      if (members > 1) v[p] = sw_load4<A>(a1 + row + i);
+      if (post) r[p] = *reinterpret_cast<const float4*>(residual + row + i);
+    }
+  }
+  if (results && post) {
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const int i = (p * 256 + threadIdx.x) * 4;
+      if (i >= width) continue;
+      const float* base = results + row + i;
+      int j = 0;
+      for (; j + 4 <= index; j += 4) {      // four earlier results requested together, added in ascending order
+        float4 h[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) h[q] = *reinterpret_cast<const float4*>(base + (size_t)(j + q) * result_stride);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float cj = coeffs[j + q];
+          s[p].x = fmaf(cj, h[q].x, s[p].x); s[p].y = fmaf(cj, h[q].y, s[p].y);
+          s[p].z = fmaf(cj, h[q].z, s[p].z); s[p].w = fmaf(cj, h[q].w, s[p].w);
+        }
+      }
+      for (; j < index; ++j) {
+        const float cj = coeffs[j];
+        const float4 h = *reinterpret_cast<const float4*>(base + (size_t)j * result_stride);
+        s[p].x = fmaf(cj, h.x, s[p].x); s[p].y = fmaf(cj, h.y, s[p].y); s[p].z = fmaf(cj, h.z, s[p].z); s[p].w = fmaf(cj, h.w, s[p].w);
+      }
+    }
+  }
+  if (members > 0) {
+    float q0 = 0.f, q1 = 0.f;
+#pragma unroll
+    for (int p = 0; p < NP; ++p) { q0 += sw_dot4(u[p]); q1 += sw_dot4(v[p]); }
+    const float r0 = 1.0f / sqrtf(block_sum(q0, red) * inv_w + eps);
+    const float r1 = members > 1 ? 1.0f / sqrtf(block_sum(q1, red) * inv_w + eps) : 0.f;
+    const float share = 1.0f / (float)members;
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const int i = (p * 256 + threadIdx.x) * 4;
+      if (i >= width) continue;
+      const float4 wa = *reinterpret_cast<const float4*>(w0 + i);
+      float4 m = make_float4(u[p].x * r0 * wa.x, u[p].y * r0 * wa.y, u[p].z * r0 * wa.z, u[p].w * r0 * wa.w);
+      if (members > 1) {
+        const float4 wb = *reinterpret_cast<const float4*>(w1 + i);
+        m.x += v[p].x * r1 * wb.x; m.y += v[p].y * r1 * wb.y; m.z += v[p].z * r1 * wb.z; m.w += v[p].w * r1 * wb.w;
+      }
+      u[p] = make_float4(m.x * share, m.y * share, m.z * share, m.w * share);
+    }
+  }
+  if (!post) {
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const int i = (p * 256 + threadIdx.x) * 4;
+      if (i < width) sw_store4<T>(y + row + i, u[p]);
+    }
+    return;
+  }
+  float sq = 0.f;
+#pragma unroll
+  for (int p = 0; p < NP; ++p) sq += sw_dot4(u[p]);
+  const float ru = 1.0f / sqrtf(block_sum(sq, red) * inv_w + eps);
+  sq = 0.f;
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    const int i = (p * 256 + threadIdx.x) * 4;
+    if (i >= width) continue;
+    const float4 p4 = *reinterpret_cast<const float4*>(post + i);
+    float4 x = make_float4(fmaf(u[p].x * ru, p4.x, r[p].x), fmaf(u[p].y * ru, p4.y, r[p].y), fmaf(u[p].z * ru, p4.z, r[p].z),
+                           fmaf(u[p].w * ru, p4.w, r[p].w));
+    if (results) {
+      *reinterpret_cast<float4*>(results + (size_t)index * result_stride + row + i) = x;
+      const float c = coeffs[index];
+      x = make_float4(fmaf(c, x.x, s[p].x), fmaf(c, x.y, s[p].y), fmaf(c, x.z, s[p].z), fmaf(c, x.w, s[p].w));
+    }
+    *reinterpret_cast<float4*>(residual + row + i) = x;
+    u[p] = x;
+    sq += sw_dot4(x);
+  }
+  if (!next) return;
+  const float rs = 1.0f / sqrtf(block_sum(sq, red) * inv_w + eps);
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    const int i = (p * 256 + threadIdx.x) * 4;
+    if (i >= width) continue;
+    const float4 n4 = *reinterpret_cast<const float4*>(next + i);
+    sw_store4<T>(y + row + i, make_float4(u[p].x * rs * n4.x, u[p].y * rs * n4.y, u[p].z * rs * n4.z, u[p].w * rs * n4.w));
+  }
+}
+
 template <typename T, typename A>
 int post_norm_add(const void* a0, const void* a1, const float* w0, const float* w1, int members, const float* post, float eps,
                   float* residual, float* results, long long result_stride, int index, const float* coeffs, const float* next,
@@ -148,8 +280,18 @@ int post_norm_add(const void* a0, const void* a1, const float* w0, const float* 
   PTL_REQUIRE((size_t)width * sizeof(float) <= 200 * 1024, "post_norm_add: rows of %d do not fit shared memory", width);
   if (rows == 0) return 0;
   // whole packets in every tensor that is walked in packets (A and T may be 2 or 4 bytes wide: 8 elements cover both)
-  const int vec = width % 8 == 0 && aligned16(a0) && (!a1 || aligned16(a1)) && aligned16(residual) && aligned16(post) &&
+  const int vec = width % 8 == 0 && aligned16(w0) && aligned16(w1) && aligned16(a0) && (!a1 || aligned16(a1)) && aligned16(residual) && aligned16(post) &&
                   aligned16(results) && aligned16(y) && aligned16(next) && result_stride % 4 == 0;
+  if (vec && width <= 4096) {
+#define PTL_SW_FAST(NP)                                                                                                         \
+    return launch_kernel("post_norm_add", post_norm_add_fast_kernel<T, A, NP>, dim3(rows), dim3(256), 0, as_stream(stream),       \
+                         (const A*)a0, (const A*)a1, w0, w1, members, post, eps, residual, results, result_stride, index, coeffs, \
+                         next, (T*)y, width)
+    if (width <= 1024) PTL_SW_FAST(1);
+    if (width <= 2048) PTL_SW_FAST(2);
+    PTL_SW_FAST(4);
+#undef PTL_SW_FAST
+  }
   const size_t smem = (size_t)width * sizeof(float);
   static SmemRaised raised;
   if (smem > 48 * 1024)

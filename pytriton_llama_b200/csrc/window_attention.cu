@@ -293,11 +293,15 @@ int head_norm_rotate_store(void* proj, int tokens, int ld, int H, int G, int d, 
 }
 
 // ------------------------------------------------------------------ means of whole blocks
+constexpr int kPoolStaged = 256;      // positions of a block whose rows are looked up once and kept in shared memory
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 pool_blocks_kernel(T* __restrict__ summary, const T* __restrict__ cache, const int* __restrict__ block_table,
                    const int* __restrict__ tok_req, const int* __restrict__ positions, const int* __restrict__ sum_slots,
-                   int bt_stride, int G, int d, int dv, int page_size, int block, int num_pages, long long num_sum_slots) {
+                   int bt_stride, int G, int d, int dv, int page_size, int block, int num_pages, long long num_sum_slots,
+                   int vec_ok) {
+  __shared__ long long s_row[kPoolStaged];     // page * page_stride + position in the page, -1: not held
   const int t = blockIdx.x;
   const long long sl = sum_slots[t];       // inputs of the step
   const int r = tok_req[t], p = positions[t];
@@ -310,19 +314,67 @@ pool_blocks_kernel(T* __restrict__ summary, const T* __restrict__ cache, const i
   T* dst = summary + (size_t)(sl / page_size) * page_stride;
   const int off = (int)(sl % page_size);
   const float inv = 1.0f / (float)block;
-  for (int idx = threadIdx.x; idx < G * (d + dv); idx += blockDim.x) {
+  const int first = p - block + 1;
+  auto row_of = [&](int j) -> long long {     // where position j lies: its page's start, and its row within a head's rows
+    const int page = bt[j / page_size];
+    return (page < 0 || page >= num_pages) ? -1 : (long long)page * (long long)page_stride;   // never follow a table entry outside the pool
+  };
+  const bool staged = block <= kPoolStaged;
+  if (staged) {
+    for (int j = threadIdx.x; j < block; j += blockDim.x) s_row[j] = row_of(first + j);
+    __syncthreads();
+  }
+  constexpr int VN = Vec16<T>::N;
+  const int step = vec_ok ? VN : 1;
+  for (int idx = threadIdx.x * step; idx < G * (d + dv); idx += blockDim.x * step) {
     const bool is_v = idx >= G * d;
     const int g = is_v ? (idx - G * d) / dv : idx / d;
     const int e = is_v ? (idx - G * d) % dv : idx % d;
     const int wd = is_v ? dv : d;
     const size_t plane = is_v ? v_plane : 0;
-    float acc = 0.f;
-    for (int j = p - block + 1; j <= p; ++j) {
-      const int page = bt[j / page_size];
-      if (page < 0 || page >= num_pages) continue;        // never follow a table entry outside the pool
-      acc += to_f32(cache[(size_t)page * page_stride + plane + ((size_t)g * page_size + j % page_size) * wd + e]);
+    const size_t head = plane + (size_t)g * page_size * wd + e;
+    float acc[VN];
+#pragma unroll
+    for (int u = 0; u < VN; ++u) acc[u] = 0.f;
+    // four positions' loads are requested together; the sums run in ascending order of position
+    for (int j0 = 0; j0 < block; j0 += 4) {
+      Vec16<T> v[4];
+      T one[4];
+      bool have[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = j0 + u;
+        have[u] = false;
+        if (j < block) {
+          const long long base = staged ? s_row[j] : row_of(first + j);
+          if (base >= 0) {
+            const T* src = cache + base + head + (size_t)((first + j) % page_size) * wd;
+            have[u] = true;
+            if (vec_ok) v[u] = load16(src); else one[u] = *src;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (have[u]) {
+          if (vec_ok) {
+#pragma unroll
+            for (int x = 0; x < VN; ++x) acc[x] += v[u].get(x);
+          } else {
+            acc[0] += to_f32(one[u]);
+          }
+        }
+      }
     }
-    dst[plane + ((size_t)g * page_size + off) * wd + e] = from_f32<T>(acc * inv);
+    T* out = dst + head + (size_t)off * wd;
+    if (vec_ok) {
+      Vec16<T> o;
+#pragma unroll
+      for (int x = 0; x < VN; ++x) o.set(x, acc[x] * inv);
+      store16(out, o);
+    } else {
+      *out = from_f32<T>(acc[0] * inv);
+    }
   }
 }
 
@@ -332,9 +384,11 @@ int pool_blocks(void* summary, const void* cache, const int* block_table, const 
                 long long num_sum_slots, void* stream) {
   PTL_REQUIRE(tokens >= 0 && G > 0 && d > 0 && dv > 0 && page_size > 0 && block > 0 && num_pages > 0, "pool_blocks: bad sizes");
   if (tokens == 0) return 0;
+  constexpr int VN = Vec16<T>::N;
+  const int vec_ok = d % VN == 0 && dv % VN == 0 && aligned16(cache) && aligned16(summary);      // every row starts a packet
   return launch_kernel("pool_blocks", pool_blocks_kernel<T>, dim3(tokens), dim3(128), 0, as_stream(stream), (T*)summary,
                        (const T*)cache, block_table, tok_req, positions, sum_slots, bt_stride, G, d, dv, page_size, block,
-                       num_pages, num_sum_slots);
+                       num_pages, num_sum_slots, vec_ok);
 }
 
 // ------------------------------------------------------------------ attention

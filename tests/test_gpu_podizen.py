@@ -51,7 +51,7 @@ def _rand(gen, *shape, scale=1.0):
 
 # ---------------------------------------------------------------------------- norm after a sub-layer, sum over depth
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("width", [40, 256, 200, 1030, 33, 4096])
+@pytest.mark.parametrize("width", [40, 256, 200, 1030, 33, 2048, 4096, 8200])
 def test_post_norm_residual_depth_sum_and_next_norm(ops, dtype, width):
     g = torch.Generator().manual_seed(width)
     dt, T, ref = DTYPES[dtype], 13, TorchOps()
