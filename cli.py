@@ -20,7 +20,7 @@ from typing import List, Optional
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(description="Generate with the B200 engine (any registered architecture: Llama, Tibepel)")
+    ap = argparse.ArgumentParser(description="Generate with the B200 engine (any registered architecture: Llama, Tibepel, Lilenex, Sogalix, Podizen)")
     ap.add_argument("--checkpoints_dir", help="model folder: config.json and model.safetensors")
     ap.add_argument("--random_weights", metavar="DIR", help="write a random-weights model folder here and use it")
     ap.add_argument("--config", help="config.json for --random_weights")
