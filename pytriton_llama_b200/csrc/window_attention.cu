@@ -30,7 +30,8 @@
 //
 // head_norm_rotate_store, per token, on [T, q | k | v | ...]: every q and k head divided by its own root mean square
 // and multiplied by the weight [d] of its kind (eps > 0), entries i and i + rot/2 of a head turned by
-// float(position) * inv_freq[i]; in place, k and v to the token's slot.  A warp per head.
+// position * inv_freq[i] (the table float32 or float64, the product and its sine and cosine in 64 bits, once per token
+// and pair); in place, k and v to the token's slot.  A warp per head.
 //
 // pool_blocks, per token with a slot in `summary`: the mean over the P positions that end with the token's own of
 // the keys and of the values in the cache, added in ascending order of position and divided by P.
@@ -211,8 +212,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 head_norm_rotate_store_kernel(T* __restrict__ proj, int ld, int H, int G, int d, int dv, const float* __restrict__ wq,
                               const float* __restrict__ wk, float eps, const int* __restrict__ positions,
-                              const float* __restrict__ inv_freq, int rot, const int* __restrict__ slots, T* __restrict__ cache,
-                              int page_size, long long num_slots) {
+                              const void* __restrict__ inv_freq, int freq64, int rot, const int* __restrict__ slots,
+                              T* __restrict__ cache, int page_size, long long num_slots) {
   extern __shared__ float hn_smem[];       // cos[rot/2], sin[rot/2], then d floats per warp
   const int t = blockIdx.x;
   const int half = rot / 2;
@@ -220,8 +221,16 @@ head_norm_rotate_store_kernel(T* __restrict__ proj, int ld, int H, int G, int d,
   float* cs = hn_smem;
   float* sn = hn_smem + half;
   float* buf = hn_smem + 2 * half + warp * d;
-  const float pos = (float)positions[t];   // an input of the step, not a result of the kernel before
-  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], sn + j, cs + j);
+  // (the angle itself in 64 bits: a float32 product of a position in the thousands and a frequency is off by up to
+  // 1e-4 radians, which float32 logits show; this runs once per token and pair)
+  const double pos = (double)positions[t];   // an input of the step, not a result of the kernel before
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    double s64, c64;
+    const double f = freq64 ? reinterpret_cast<const double*>(inv_freq)[j] : (double)reinterpret_cast<const float*>(inv_freq)[j];
+    sincos(pos * f, &s64, &c64);
+    sn[j] = (float)s64;
+    cs[j] = (float)c64;
+  }
   pdl_wait();
   pdl_launch_dependents();
   __syncthreads();
@@ -275,8 +284,8 @@ head_norm_rotate_store_kernel(T* __restrict__ proj, int ld, int H, int G, int d,
 
 template <typename T>
 int head_norm_rotate_store(void* proj, int tokens, int ld, int H, int G, int d, int dv, const float* wq, const float* wk, float eps,
-                           const int* positions, const float* inv_freq, int rot, const int* slots, void* cache, int page_size,
-                           long long num_slots, void* stream) {
+                           const int* positions, const void* inv_freq, int freq64, int rot, const int* slots, void* cache,
+                           int page_size, long long num_slots, void* stream) {
   PTL_REQUIRE(tokens >= 0 && H > 0 && G >= 0 && d > 0 && dv > 0 && page_size > 0, "head_norm_rotate_store: bad sizes");
   PTL_REQUIRE(ld >= (H + G) * d + G * dv, "head_norm_rotate_store: rows of %d elements are too short", ld);
   PTL_REQUIRE(eps <= 0.f || (wq && (G == 0 || wk)), "head_norm_rotate_store: the norm needs its weights");
@@ -288,7 +297,7 @@ int head_norm_rotate_store(void* proj, int tokens, int ld, int H, int G, int d, 
   if (smem > 48 * 1024)
     if (int rc = raise_shared_memory("head_norm_rotate_store", head_norm_rotate_store_kernel<T>, 200 * 1024, raised)) return rc;
   return launch_kernel("head_norm_rotate_store", head_norm_rotate_store_kernel<T>, dim3(tokens), dim3(256), smem, as_stream(stream),
-                       (T*)proj, ld, H, G, d, dv, wq, wk, eps, positions, rot > 0 ? inv_freq : nullptr, rot,
+                       (T*)proj, ld, H, G, d, dv, wq, wk, eps, positions, rot > 0 ? inv_freq : nullptr, freq64, rot,
                        G > 0 ? slots : nullptr, (T*)cache, page_size, num_slots);
 }
 
@@ -774,11 +783,11 @@ int window_attention(void* out, const void* q, const void* cache, const int* blo
                                        sum_bt_stride, sum_pages, stream);                                                          \
   }                                                                                                                                \
   PTL_EXPORT int ptl_head_norm_rotate_store##SUFFIX(void* proj, int tokens, int ld, int H, int G, int d, int dv, const float* wq,   \
-                                                    const float* wk, float eps, const int* positions, const float* inv_freq,       \
-                                                    int rot, const int* slots, void* cache, int page_size, long long num_slots,    \
-                                                    void* stream) {                                                                \
-    return ptl::head_norm_rotate_store<TYPE>(proj, tokens, ld, H, G, d, dv, wq, wk, eps, positions, inv_freq, rot, slots, cache,    \
-                                             page_size, num_slots, stream);                                                        \
+                                                    const float* wk, float eps, const int* positions, const void* inv_freq,        \
+                                                    int freq64, int rot, const int* slots, void* cache, int page_size,             \
+                                                    long long num_slots, void* stream) {                                           \
+    return ptl::head_norm_rotate_store<TYPE>(proj, tokens, ld, H, G, d, dv, wq, wk, eps, positions, inv_freq, freq64, rot, slots,   \
+                                             cache, page_size, num_slots, stream);                                                 \
   }                                                                                                                                \
   PTL_EXPORT int ptl_pool_blocks##SUFFIX(void* summary, const void* cache, const int* block_table, const int* tok_req,              \
                                          const int* positions, const int* sum_slots, int tokens, int bt_stride, int G, int d,      \

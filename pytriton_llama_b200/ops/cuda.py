@@ -50,8 +50,8 @@ _SIGNATURES = {
     "ptl_window_attention": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                              _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _c_int, _c_f, _c_int, _c_f, _c_int,
                              _c_int, _ptr, _ptr, _c_int, _c_int, _ptr],
-    "ptl_head_norm_rotate_store": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _c_int, _ptr,
-                                   _ptr, _c_int, _c_ll, _ptr],
+    "ptl_head_norm_rotate_store": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _c_int, _c_int,
+                                   _ptr, _ptr, _c_int, _c_ll, _ptr],
     "ptl_pool_blocks": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _ptr],
     "ptl_post_norm_add": [_ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _c_f, _ptr, _ptr, _c_ll, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int,
                           _c_int, _ptr],
@@ -1235,13 +1235,17 @@ class CudaOps:
                                cache: Optional[torch.Tensor], page_size: int) -> None:
         """On proj [T, q | k | v | ...] (H heads of d, G of d, G of dv; G = 0: nothing is stored), in place: every q and k
         head divided by its own root mean square and multiplied by the weight [d] of its kind (eps > 0), entries i and
-        i + rot/2 of every head turned by position * inv_freq[i]; k and v go to the tokens' slots of a cache whose pages
-        hold keys, then values."""
+        i + rot/2 of every head turned by position * inv_freq[i] (``inv_freq`` float32 or float64; the angle is worked
+        out in 64 bits either way); k and v go to the tokens' slots of a cache whose pages hold keys, then values."""
         self._want(proj, "proj")
         self._want(positions, "positions", torch.int32)
-        for name, t in (("q norm", q_norm), ("k norm", k_norm), ("inv_freq", inv_freq)):
+        for name, t in (("q norm", q_norm), ("k norm", k_norm)):
             if t is not None:
                 self._want(t, name, torch.float32)
+        if inv_freq is not None:
+            self._want(inv_freq, "inv_freq")
+            if inv_freq.dtype not in (torch.float32, torch.float64):
+                raise KernelError("head_norm_rotate_store: frequencies are float32 or float64")
         if eps > 0 and (q_norm.numel() != d or (G and k_norm.numel() != d)):
             raise KernelError("head_norm_rotate_store: the norm weights have the size of a head")
         num_slots = 0
@@ -1255,7 +1259,8 @@ class CudaOps:
             raise KernelError("head_norm_rotate_store: fewer frequencies than pairs")
         fn = getattr(self.lib, "ptl_head_norm_rotate_store" + _suffix(proj.dtype))
         self._check(fn(_p(proj), proj.shape[0], proj.shape[1], H, G, d, dv, _p(q_norm), _p(k_norm), float(eps), _p(positions),
-                       _p(inv_freq), int(rot) if inv_freq is not None else 0, _p(slots) if G else None, _p(cache) if G else None,
+                       _p(inv_freq), int(inv_freq is not None and inv_freq.dtype == torch.float64),
+                       int(rot) if inv_freq is not None else 0, _p(slots) if G else None, _p(cache) if G else None,
                        page_size, num_slots, self._stream()))
 
     def pool_blocks(self, cache: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor, positions: torch.Tensor,

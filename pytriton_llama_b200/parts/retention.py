@@ -58,7 +58,8 @@ class Retention(Part):
         ops = self.rt.ops
         H, d, dv = self.heads, self.d, self.dv
         proj = ops.linear(x, self.w_qkvg)                                     # [T, q | k | v | gate]
-        inv_freq, rot = self.position.rotary_table() if self.position is not None else (None, 0)
+        inv_freq, rot = (None, 0) if self.position is None else \
+            self.position.rotary_table64() if hasattr(self.position, "rotary_table64") else self.position.rotary_table()
         if rot:
             # q and k are 2 * heads heads of the same size side by side; nothing is normed or stored
             ops.head_norm_rotate_store(proj, 2 * H, 0, d, dv, None, None, 0.0, ctx.positions, inv_freq, rot, None, None, 1)

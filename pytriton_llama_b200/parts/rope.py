@@ -62,6 +62,20 @@ class RotaryPosition(Part):
         if key not in shared:
             shared[key] = rope_inverse_frequencies(self.head_dim, float(p["theta"]), scaling, self.rot).to(runtime.device)
         self.inv_freq = shared[key]
+        # the same frequencies in 64 bits, for kernels that work the angle out in 64 bits (an unscaled table is made
+        # anew from theta; a scaled one is the float32 table widened)
+        key64 = key + ("f64",)
+        if key64 not in shared:
+            if scaling is None or scaling.get("rope_type", "default") == "default":
+                exact = float(p["theta"]) ** (-torch.arange(0, self.rot, 2, dtype=torch.float64) / self.rot)
+            else:
+                exact = self.inv_freq.detach().cpu().to(torch.float64)
+            shared[key64] = exact.to(runtime.device)
+        self.inv_freq64 = shared[key64]
+
+    def rotary_table64(self) -> Tuple[torch.Tensor, int]:
+        """(float64 inv_freq [rot/2], rot)."""
+        return self.inv_freq64, self.rot
 
     def rotary_table(self) -> Optional[Tuple[torch.Tensor, int]]:
         return self.inv_freq, self.rot

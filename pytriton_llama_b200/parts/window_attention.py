@@ -149,6 +149,8 @@ class WindowAttention(Part):
             raise ValueError("a layer with keys and values of its own writes its cache entry, one without reads another's")
         proj = ops.linear(x, self.w_in)                   # [T, q (| k | v) (| gate)]
         table = self.position.rotary_table() if self.position is not None and hasattr(self.position, "rotary_table") else (None, 0)
+        if table is not None and table[1] and hasattr(self.position, "rotary_table64") and (self.per_head_norm or self.qk_norm_eps <= 0):
+            table = self.position.rotary_table64()
         G = self.kv_heads if self.own_kv else 0
         if table is not None and (self.per_head_norm or self.qk_norm_eps <= 0):
             # halves of a head turned against each other (or nothing turned), a norm per head (or none)
