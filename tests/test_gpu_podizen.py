@@ -175,13 +175,26 @@ POOL_SHAPES = [   # H, G, d, dv, page, window, block, bias, gate
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,d,dv,page,window,block,bias,gate", POOL_SHAPES)
 def test_block_means_and_attention_with_bias_gate_and_pooled_blocks(ops, dtype, H, G, d, dv, page, window, block, bias, gate):
+    # a prompt that passes many blocks, single tokens, portions
+    _pooled_attention_case(ops, dtype, H, G, d, dv, page, window, block, bias, gate, [300, 1, 37, 1, 2], [0, 190, 61, 3, 254])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,d,window,block", [(4, 2, 64, 30, 4), (2, 1, 128, 17, 3), (4, 4, 64, 200, 2)])
+def test_hundreds_of_block_means_fill_several_key_tiles(ops, dtype, H, G, d, window, block):
+    """More block means than one key tile of the prompt kernels holds, in a whole prompt and in a portion that follows
+    700 cached positions (whose means earlier steps made), beside a single token far out."""
+    _pooled_attention_case(ops, dtype, H, G, d, d, 16, window, block, 8.0, True, [900, 150, 1], [0, 700, 820])
+
+
+def _pooled_attention_case(ops, dtype, H, G, d, dv, page, window, block, bias, gate, q_lens, starts):
     g = torch.Generator().manual_seed(H * 100 + d + block)
     dt, ref = DTYPES[dtype], TorchOps()
-    q_lens, starts = [300, 1, 37, 1, 2], [0, 190, 61, 3, 254]      # a prompt that passes many blocks, single tokens, portions
-    cd, cc = _ctx(q_lens, starts, [0, 1, 2, 3, 4], "cuda:0"), _ctx(q_lens, starts, [0, 1, 2, 3, 4], "cpu")
+    R = len(q_lens)
+    cd, cc = _ctx(q_lens, starts, list(range(R)), "cuda:0"), _ctx(q_lens, starts, list(range(R)), "cpu")
     T = sum(q_lens)
     pages = sum(-(-(s + n) // page) for s, n in zip(starts, q_lens)) + 3
-    bt, slots = _paged(g, q_lens, starts, page, pages, width=-(-300 // page) + 2)
+    bt, slots = _paged(g, q_lens, starts, page, pages, width=max(-(-(s + n) // page) for s, n in zip(starts, q_lens)) + 2)
     gate_col = H * d + G * (d + dv)
     proj = _rand(g, T, gate_col + H * dv).to(dt)
     cache = _rand(g, pages, G * page * (d + dv), scale=0.5).to(dt)
